@@ -48,11 +48,16 @@ class CacheError(RuntimeError):
 @dataclass(frozen=True)
 class PagedKV:
     """A layer that keeps keys and values per token.  ``window``: how many keys a query sees
-    (None = all)."""
+    (None = all); with a window, the first ``keep_first`` keys are seen from everywhere and
+    their pages never go back.  ``every`` > 1: one entry per so many tokens (entry b belongs to
+    the tokens ``b * every ..``, written when the last of them has come), for layers that keep
+    a pooled key and value per block of tokens."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    keep_first: int = 0
+    every: int = 1
 
 
 @dataclass(frozen=True)
@@ -74,7 +79,7 @@ def _core():
         P, I, K = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
         IP = ctypes.POINTER(ctypes.c_int)
         sigs = {
-            "llm_cache_new": (P, [I, IP, IP, I, I, I, I]),
+            "llm_cache_new": (P, [I, IP, IP, I, I, I, I, IP, IP]),
             "llm_cache_delete": (None, [P]),
             "llm_cache_open": (I, [P, K]),
             "llm_cache_has": (I, [P, K]),
@@ -200,7 +205,10 @@ class CacheManager:
                 if g is None:
                     g = len(self.groups)
                     by_need[need] = g
-                    self.groups.append(_Group(need, n_pages))
+                    # (a group with one entry per `every` tokens needs that many times fewer
+                    # pages, and one more per request for its last, partly filled page)
+                    self.groups.append(_Group(need, n_pages if need.every == 1 else
+                                              -(-n_pages // need.every) + max_requests))
                 self._where[i] = (g, len(self.groups[g].entries))
                 self.groups[g].entries.append(i)
             elif isinstance(need, FixedState):
@@ -219,8 +227,10 @@ class CacheManager:
         self._lib = _core()
         pages = (ctypes.c_int * max(G, 1))(*[g.n_pages for g in self.groups])
         windows = (ctypes.c_int * max(G, 1))(*[g.need.window or 0 for g in self.groups])
+        keeps = (ctypes.c_int * max(G, 1))(*[g.need.keep_first for g in self.groups])
+        everys = (ctypes.c_int * max(G, 1))(*[g.need.every for g in self.groups])
         self._c = self._lib.llm_cache_new(G, pages, windows, page_size, max_requests, max_context,
-                                          int(bool(self._state_need)))
+                                          int(bool(self._state_need)), keeps, everys)
         if not self._c:
             raise CacheError("the cache core refused these sizes")
         self._keys: Dict[Any, int] = {}            # open requests: id -> the core's 64-bit key

@@ -4,6 +4,7 @@ from .registry import (config_class, load_config, load_spec, read_config_json,
 from .qwen3 import Qwen3Config
 from .vunasun import VunasunConfig
 from .runidra import RunidraConfig
+from .pemolorn import PemolornConfig
 
 register_architecture(Qwen3Config.architecture, Qwen3Config, Qwen3Config.model_type, replace=True)
 register_architecture(VunasunConfig.architecture, VunasunConfig, VunasunConfig.model_type,
@@ -11,7 +12,10 @@ register_architecture(VunasunConfig.architecture, VunasunConfig, VunasunConfig.m
 register_architecture(RunidraConfig.architecture, RunidraConfig, RunidraConfig.model_type,
                       replace=True)
 
+register_architecture(PemolornConfig.architecture, PemolornConfig, PemolornConfig.model_type,
+                      replace=True)
+
 __all__ = ["ConfigError", "LayerCall", "LayerSpec", "ModelSpec", "PartSpec", "Qwen3Config",
-           "VunasunConfig", "RunidraConfig",
+           "VunasunConfig", "RunidraConfig", "PemolornConfig",
            "config_class", "load_config", "load_spec", "read_config_json",
            "register_architecture", "registered_architectures", "resolve_architecture"]

@@ -10,6 +10,11 @@
 // (a key that has no value: it takes weight and gives nothing); `vd`, how many of a value
 // row's first channels are summed and written (out is [rows][Hq][vd]; the rest of a value row is
 // not read), for caches whose values are a prefix of their keys.
+// Two more: `keep_first`, the first so many keys of a sequence are seen from every later position
+// although a window has passed them; and a second, pooled cache (`pool` > 0) that holds one key
+// and value per block of `pool` positions, of which a row sees the blocks that end at or before
+// pos - window.  Pooled blocks, kept keys, the window's keys and the sink share one softmax; they
+// are visited in that order, in tiles of 32 aligned to entry 0 and to absolute positions.
 #include "common.cuh"
 
 namespace {
@@ -40,12 +45,23 @@ template <> struct Vec8<bf16> {
 
 // VEC: the head size is a multiple of 8, so a key row is read in 16-byte (32-byte) pieces.
 // NACC: 32-channel pieces of a value row that a lane sums (vd <= 32 * NACC)
+// the second cache of a layer with pooled blocks (null k: none)
+struct PooledSource {
+  const void *k, *v;
+  long long page_stride;
+  const int* table;
+  int table_stride, pool;
+};
+
+// VEC: the head size is a multiple of 8, so a key row is read in 16-byte (32-byte) pieces.
+// NACC: 32-channel pieces of a value row that a lane sums (vd <= 32 * NACC)
 template <typename T, bool VEC, int NACC>
 __global__ void __launch_bounds__(WARPS * 32) attention_generic_kernel(
     const T* __restrict__ q, T* __restrict__ out, const T* __restrict__ k_cache,
     const T* __restrict__ v_cache, long long page_stride, const int* __restrict__ block_table,
     int table_stride, const int* __restrict__ row_slot, const int* __restrict__ row_pos, int rows,
-    int Hq, int Hkv, int hd, int page_size, float scale, int window, const float* __restrict__ sink, int vd) {
+    int Hq, int Hkv, int hd, int page_size, float scale, int window, const float* __restrict__ sink, int vd,
+    int keep_first, const PooledSource pooled) {
   __shared__ float q_s[WARPS][MAX_HD];
   const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * WARPS + warp_in_block;
@@ -66,15 +82,11 @@ __global__ void __launch_bounds__(WARPS * 32) attention_generic_kernel(
 #pragma unroll
   for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
 
-  for (int base = (lo / 32) * 32; base <= pos; base += 32) {
-    const int p = base + lane;
-    const bool valid = p >= lo && p <= pos;
-    long long off = 0;  // element offset of this lane's key row inside the layer's cache
+  // one tile: this lane's entry is visible or not; kc / vc and off say where its rows lie
+  auto tile = [&](bool valid, const T* kc, const T* vc, long long off) {
     float s = -INFINITY;
     if (valid) {
-      const int page = table[p / page_size];
-      off = (long long)page * page_stride + ((long long)kvh * page_size + p % page_size) * hd;
-      const T* kr = k_cache + off;
+      const T* kr = kc + off;
       float d = 0.f;
       if (VEC) {
         for (int i = 0; i < hd; i += 8) {
@@ -88,6 +100,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_generic_kernel(
       }
       s = d * scale;
     }
+    const unsigned mask = __ballot_sync(0xffffffffu, valid);
+    if (mask == 0) return;
     const float m_new = fmaxf(m, warp_max(s));
     const float w = valid ? expf(s - m_new) : 0.f;
     const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
@@ -95,18 +109,50 @@ __global__ void __launch_bounds__(WARPS * 32) attention_generic_kernel(
 #pragma unroll
     for (int i = 0; i < NACC; ++i) acc[i] *= corr;
     m = m_new;
-    const unsigned mask = __ballot_sync(0xffffffffu, valid);
     for (int j = 0; j < 32; ++j) {
       if (!((mask >> j) & 1u)) continue;
       const float wj = __shfl_sync(0xffffffffu, w, j);
       const long long oj = __shfl_sync(0xffffffffu, off, j);
-      const T* vr = v_cache + oj;
+      const T* vr = vc + oj;
 #pragma unroll
       for (int i = 0; i < NACC; ++i) {
         const int d = lane + 32 * i;
         if (d < vd) acc[i] = fmaf(wj, to_f32(vr[d]), acc[i]);
       }
     }
+  };
+
+  if (pooled.k != nullptr && window > 0) {
+    // blocks b with b * pool + pool - 1 <= pos - window
+    const int seen = pos - window + 1 >= pooled.pool ? (pos - window + 1) / pooled.pool : 0;
+    const int* ptable = pooled.table + (size_t)row_slot[t] * pooled.table_stride;
+    for (int base = 0; base < seen; base += 32) {
+      const int b = base + lane;
+      const bool valid = b < seen;
+      long long off = 0;
+      if (valid)
+        off = (long long)ptable[b / page_size] * pooled.page_stride +
+              ((long long)kvh * page_size + b % page_size) * hd;
+      tile(valid, (const T*)pooled.k, (const T*)pooled.v, off);
+    }
+  }
+  // the kept first keys that the window has passed (those inside it are met below)
+  const int kept = keep_first < lo ? keep_first : lo;
+  for (int base = 0; base < kept; base += 32) {
+    const int p = base + lane;
+    const bool valid = p < kept;
+    long long off = 0;
+    if (valid)
+      off = (long long)table[p / page_size] * page_stride + ((long long)kvh * page_size + p % page_size) * hd;
+    tile(valid, k_cache, v_cache, off);
+  }
+  for (int base = (lo / 32) * 32; base <= pos; base += 32) {
+    const int p = base + lane;
+    const bool valid = p >= lo && p <= pos;
+    long long off = 0;  // element offset of this lane's key row inside the layer's cache
+    if (valid)
+      off = (long long)table[p / page_size] * page_stride + ((long long)kvh * page_size + p % page_size) * hd;
+    tile(valid, k_cache, v_cache, off);
   }
   if (sink) l += expf(sink[h] - m);     // (m is finite: a row sees at least its own key)
   const float inv = 1.0f / l;
@@ -119,23 +165,33 @@ __global__ void __launch_bounds__(WARPS * 32) attention_generic_kernel(
 }
 }  // namespace
 
-LLM_EXPORT int llm_attention_generic(const void* q, void* out, const void* k_cache,
-                                     const void* v_cache, int dtype, long long page_stride,
-                                     const int* block_table, int table_stride, const int* row_slot,
-                                     const int* row_pos, int rows, int Hq, int Hkv, int hd,
-                                     int page_size, float scale, int window, const float* sink, int vd,
-                                     cudaStream_t stream) {
+// keep_first and the pooled cache (pk_cache null: none) as described at the top of this file
+LLM_EXPORT int llm_attention_generic_ext(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                         int dtype, long long page_stride, const int* block_table,
+                                         int table_stride, const int* row_slot, const int* row_pos, int rows,
+                                         int Hq, int Hkv, int hd, int page_size, float scale, int window,
+                                         const float* sink, int vd, int keep_first, const void* pk_cache,
+                                         const void* pv_cache, long long p_page_stride, const int* p_table,
+                                         int p_table_stride, int pool, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vd <= 0) vd = hd;
   if (hd > MAX_HD || hd <= 0 || vd > hd || Hkv <= 0 || Hq % Hkv != 0) return LLM_ERR_UNSUPPORTED;
+  if (keep_first < 0 || (pk_cache != nullptr && (pool <= 0 || window <= 0 || !pv_cache || !p_table)))
+    return LLM_ERR_ARGUMENT;
+  PooledSource pooled;
+  pooled.k = pk_cache, pooled.v = pv_cache, pooled.page_stride = p_page_stride, pooled.table = p_table;
+  pooled.table_stride = p_table_stride, pooled.pool = pool;
   const bool vec = hd % 8 == 0 && (page_stride % 8) == 0 &&
-                   (((uintptr_t)k_cache | (uintptr_t)v_cache) & 31) == 0;
+                   (((uintptr_t)k_cache | (uintptr_t)v_cache) & 31) == 0 &&
+                   (pk_cache == nullptr ||
+                    ((p_page_stride % 8) == 0 && (((uintptr_t)pk_cache | (uintptr_t)pv_cache) & 31) == 0));
   const long long items = (long long)rows * Hq;
   const int blocks = (int)((items + WARPS - 1) / WARPS);
 #define GENERIC(T, V, N)                                                                            \
   attention_generic_kernel<T, V, N><<<blocks, WARPS * 32, 0, stream>>>(                             \
       (const T*)q, (T*)out, (const T*)k_cache, (const T*)v_cache, page_stride, block_table,         \
-      table_stride, row_slot, row_pos, rows, Hq, Hkv, hd, page_size, scale, window, sink, vd)
+      table_stride, row_slot, row_pos, rows, Hq, Hkv, hd, page_size, scale, window, sink, vd,       \
+      keep_first, pooled)
 #define GENERIC_N(T, V)                                  \
   do {                                                   \
     if (vd <= 128) GENERIC(T, V, 4);                     \
@@ -152,4 +208,15 @@ LLM_EXPORT int llm_attention_generic(const void* q, void* out, const void* k_cac
 #undef GENERIC_N
 #undef GENERIC
   return launch_status();
+}
+
+LLM_EXPORT int llm_attention_generic(const void* q, void* out, const void* k_cache,
+                                     const void* v_cache, int dtype, long long page_stride,
+                                     const int* block_table, int table_stride, const int* row_slot,
+                                     const int* row_pos, int rows, int Hq, int Hkv, int hd,
+                                     int page_size, float scale, int window, const float* sink, int vd,
+                                     cudaStream_t stream) {
+  return llm_attention_generic_ext(q, out, k_cache, v_cache, dtype, page_stride, block_table, table_stride,
+                                   row_slot, row_pos, rows, Hq, Hkv, hd, page_size, scale, window, sink, vd, 0,
+                                   nullptr, nullptr, 0, nullptr, 0, 0, stream);
 }

@@ -8,7 +8,10 @@
 // block ids per sequence, all-or-nothing allocation that refuses with "needed / free" before it
 // changes anything, and separate classes of storage for layers that keep every key and layers that
 // keep a window of them.  Here every group of layers with the same need has a pool and a table of
-// its own; a group with a window gives a page back as soon as no later query can reach a key in it.
+// its own; a group with a window gives a page back as soon as no later query can reach a key in it
+// (the pages that hold a group's first `keep_first` keys stay: such layers see them from anywhere).
+// A group with `every` > 1 keeps one entry per `every` tokens, written when the last of them has
+// come: entry b belongs to the tokens b * every .. b * every + every - 1.
 //
 // Requests are named by 64-bit keys that the caller chooses.  Every function returns 0 or a
 // count on success and a negative code on misuse (the caller turns it into an exception); nothing
@@ -82,6 +85,8 @@ struct Request {
 struct Group {
   Pool pool;
   int window;                            // 0: every key is kept
+  int keep_first = 0;                    // with a window: the first so many keys are kept as well
+  int every = 1;                         // tokens per entry of this group
   // changes of the device table not yet taken: one value per cell, the last one wins
   std::vector<int> pending;              // [max_requests * pages_per_request]
   std::vector<char> dirty;
@@ -109,9 +114,18 @@ struct Core {
     const int first_key = length - g.window + 1;
     return (first_key > 0 ? first_key : 0) / page_size;
   }
+  // pages that hold the keys a window never passes
+  int kept_pages(const Group& g) const {
+    return g.window > 0 ? (g.keep_first + page_size - 1) / page_size : 0;
+  }
+  // pages of group g that hold the entries of `length` tokens
+  int pages_for(const Group& g, long long length) const {
+    const long long entries = length / g.every;
+    return (int)((entries + page_size - 1) / page_size);
+  }
   void needed(const Request& r, int new_tokens, int* out) const {
-    const int want = (r.length + new_tokens + page_size - 1) / page_size;
     for (size_t g = 0; g < groups.size(); ++g) {
+      const int want = pages_for(groups[g], (long long)r.length + new_tokens);
       const int have = (int)r.pages[g].size();
       out[g] = want > have ? want - have : 0;
     }
@@ -122,11 +136,12 @@ struct Core {
 
 extern "C" {
 
+// keep_first and every may be null (no kept keys, an entry per token)
 Core* llm_cache_new(int n_groups, const int* n_pages, const int* window, int page_size, int max_requests,
-                    int max_context, int has_state) {
+                    int max_context, int has_state, const int* keep_first, const int* every) {
   if (n_groups < 0 || page_size <= 0 || max_requests <= 0 || max_context <= 0) return nullptr;
   for (int g = 0; g < n_groups; ++g)
-    if (n_pages[g] <= 0) return nullptr;
+    if (n_pages[g] <= 0 || (every && every[g] < 1) || (keep_first && keep_first[g] < 0)) return nullptr;
   Core* c = new Core();
   c->page_size = page_size;
   c->max_requests = max_requests;
@@ -135,6 +150,10 @@ Core* llm_cache_new(int n_groups, const int* n_pages, const int* window, int pag
   c->has_state = has_state;
   for (int g = 0; g < n_groups; ++g)
     c->groups.emplace_back(n_pages[g], window[g], max_requests * c->pages_per_request);
+  for (int g = 0; g < n_groups; ++g) {
+    if (keep_first) c->groups[g].keep_first = keep_first[g];
+    if (every) c->groups[g].every = every[g];
+  }
   for (int s = 0; s < max_requests; ++s) c->free_slots.push_back(s);
   return c;
 }
@@ -189,6 +208,16 @@ int llm_cache_pages_needed(Core* c, int64_t key, int new_tokens, int* out) {
   if (it == c->requests.end()) return E_UNKNOWN;
   c->needed(it->second, new_tokens, out);
   return 0;
+}
+
+// pages each group needs for a request that holds nothing yet and gets new_tokens
+int llm_cache_pages_for_new(Core* c, int new_tokens, int* out) {
+  for (size_t g = 0; g < c->groups.size(); ++g) out[g] = c->pages_for(c->groups[g], new_tokens);
+  return 0;
+}
+
+int llm_cache_group_every(Core* c, int group) {
+  return group >= 0 && group < (int)c->groups.size() ? c->groups[group].every : 1;
 }
 
 // Room for every (request, new tokens) of a step, or nothing changed.  Returns 0; 1 when the
@@ -246,19 +275,21 @@ int llm_cache_advance(Core* c, int64_t key, int n) {
   if (it == c->requests.end()) return E_UNKNOWN;
   Request& r = it->second;
   for (size_t g = 0; g < c->groups.size(); ++g)
-    if ((long long)r.length + n > (long long)r.pages[g].size() * c->page_size) return E_PAST_RESERVED;
+    if (c->pages_for(c->groups[g], (long long)r.length + n) > (int)r.pages[g].size()) return E_PAST_RESERVED;
   r.length += n;
   for (size_t g = 0; g < c->groups.size(); ++g) {
     Group& grp = c->groups[g];
     int keep_from = c->first_needed_page(grp, r.length);
     if (keep_from > (int)r.pages[g].size()) keep_from = (int)r.pages[g].size();
-    if (keep_from > r.first_live[g]) {
-      const int gone = keep_from - r.first_live[g];
-      const int rc = grp.pool.release(r.pages[g].data() + r.first_live[g], gone);
+    // (pages in front of first_live are gone, except the first kept_pages, which stay)
+    const int from = r.first_live[g] > c->kept_pages(grp) ? r.first_live[g] : c->kept_pages(grp);
+    if (keep_from > from) {
+      const int gone = keep_from - from;
+      const int rc = grp.pool.release(r.pages[g].data() + from, gone);
       if (rc) return rc;
       c->counters[1] += gone;
       c->counters[2] += gone;
-      for (int j = r.first_live[g]; j < keep_from; ++j) {
+      for (int j = from; j < keep_from; ++j) {
         r.pages[g][j] = -1;
         grp.set(r.slot * c->pages_per_request + j, -1);
       }
@@ -276,15 +307,17 @@ int llm_cache_truncate(Core* c, int64_t key, int length, int* info) {
   Request& r = it->second;
   if (length > r.length || length < 0) return E_LENGTHEN;
   if (c->has_state && length < r.length) return E_STATE_REWIND;
-  for (size_t g = 0; g < c->groups.size(); ++g)
-    if (c->first_needed_page(c->groups[g], length) < r.first_live[g]) {
+  for (size_t g = 0; g < c->groups.size(); ++g) {
+    const int kept = c->kept_pages(c->groups[g]), first = c->first_needed_page(c->groups[g], length);
+    if ((first > kept ? first : kept) < r.first_live[g]) {
       info[0] = (int)g;
       return E_WINDOW_GONE;
     }
-  const int keep = (length + c->page_size - 1) / c->page_size;
+  }
   std::vector<int> gone;
   for (size_t g = 0; g < c->groups.size(); ++g) {
     Group& grp = c->groups[g];
+    const int keep = c->pages_for(grp, length);
     gone.clear();
     for (int j = keep; j < (int)r.pages[g].size(); ++j) {
       if (r.pages[g][j] >= 0) gone.push_back(r.pages[g][j]);

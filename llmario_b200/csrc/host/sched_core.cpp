@@ -30,6 +30,8 @@ int llm_cache_info(Core* c, int64_t key, int* slot, int* length);
 int llm_cache_free_slots(Core* c);
 void llm_cache_free_pages(Core* c, int* out);
 int llm_cache_pages_needed(Core* c, int64_t key, int new_tokens, int* out);
+int llm_cache_pages_for_new(Core* c, int new_tokens, int* out);
+int llm_cache_group_every(Core* c, int group);
 int llm_cache_close(Core* c, int64_t key);
 int llm_cache_pages_of(Core* c, int64_t key, int group, int* out, int cap);
 }
@@ -72,7 +74,7 @@ struct Sched {
     if (opened && llm_cache_has(cache, r.key)) {
       llm_cache_pages_needed(cache, r.key, count, need.data());
     } else {
-      for (int g = 0; g < n_groups; ++g) need[g] = (count + page_size - 1) / page_size;
+      llm_cache_pages_for_new(cache, count, need.data());     // (a group may keep fewer entries than tokens)
     }
     return need;
   }
@@ -90,13 +92,16 @@ struct Sched {
     opened = opened && llm_cache_has(cache, r.key);
     if (fits(pages_for(r, n, opened), free)) return n;
     if (n_groups == 0) return n;
-    int have = 0, held = 0, slot = 0;
-    if (opened) {
-      llm_cache_info(cache, r.key, &slot, &have);
-      held = llm_cache_pages_of(cache, r.key, 0, nullptr, 0);
+    int have = 0, slot = 0;
+    if (opened) llm_cache_info(cache, r.key, &slot, &have);
+    // every group bounds the tokens the request can hold: its pages times the tokens of a page
+    // (a group with one entry per `every` tokens holds that many times more)
+    long long room = n;
+    for (int g = 0; g < n_groups; ++g) {
+      const int held = opened ? llm_cache_pages_of(cache, r.key, g, nullptr, 0) : 0;
+      const long long every = llm_cache_group_every(cache, g);
+      room = std::min(room, (long long)(held + free[g]) * page_size * every + (every - 1) - have);
     }
-    const int least = *std::min_element(free.begin(), free.end());
-    const long long room = (long long)(held + least) * page_size - have;
     return (int)std::max<long long>(0, std::min<long long>(n, room));
   }
   void drop_running(int64_t key) {

@@ -20,15 +20,22 @@
 namespace {
 constexpr int MAX_TOP = 16;
 
-// One warp per row.  The k-th choice is the largest logit not chosen before (the lowest index
-// among equals); the weights are a softmax in which only the chosen logits take part.
-__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ z, int z_stride, int rows, int E,
-                                                        int top, int* __restrict__ ids, float* __restrict__ wts) {
-  pdl_trigger();
-  pdl_wait();
-  const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (r >= rows) return;
-  const float* zr = z + (size_t)r * z_stride;
+// The choice of one row by one warp, from its E router outputs zr (shared or global memory).
+// mode 0: the k-th choice is the largest logit not chosen before (the lowest index among equals);
+// the weights are a softmax in which only the chosen logits take part.  mode 1: scores are the
+// softmax over all E outputs; the choice goes by score + corr[e] (the same tie rule), the weight
+// of a chosen expert is its score, not renormalised.
+__device__ __forceinline__ void choose_row(const float* zr, int E, int top, int mode, const float* __restrict__ corr,
+                                           int lane, int* __restrict__ ids, float* __restrict__ wts) {
+  float zmax = 0.f, inv_sum = 1.f;
+  if (mode == 1) {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zr[e]);
+    zmax = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) sum += expf(zr[e] - zmax);
+    inv_sum = 1.f / warp_sum(sum);
+  }
   float best[MAX_TOP];
   int pick[MAX_TOP];
   for (int k = 0; k < top; ++k) {
@@ -37,7 +44,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     for (int e = lane; e < E; e += 32) {
       bool taken = false;
       for (int j = 0; j < k; ++j) taken |= pick[j] == e;
-      const float x = zr[e];
+      const float x = mode == 1 ? expf(zr[e] - zmax) * inv_sum + (corr ? corr[e] : 0.f) : zr[e];
       if (!taken && (x > v || (x == v && e < at) || at == 0x7fffffff)) v = x, at = e;
     }
 #pragma unroll
@@ -49,13 +56,31 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     best[k] = v, pick[k] = at;
   }
   if (lane == 0) {
+    if (mode == 1) {
+      for (int k = 0; k < top; ++k) {
+        ids[k] = pick[k];
+        wts[k] = expf(zr[pick[k]] - zmax) * inv_sum;
+      }
+      return;
+    }
     float sum = 0.f;       // best[0] is the largest
     for (int k = 0; k < top; ++k) sum += expf(best[k] - best[0]);
     for (int k = 0; k < top; ++k) {
-      ids[(size_t)r * top + k] = pick[k];
-      wts[(size_t)r * top + k] = expf(best[k] - best[0]) / sum;
+      ids[k] = pick[k];
+      wts[k] = expf(best[k] - best[0]) / sum;
     }
   }
+}
+
+// One warp per row.
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ z, int z_stride, int rows, int E,
+                                                        int top, int mode, const float* __restrict__ corr,
+                                                        int* __restrict__ ids, float* __restrict__ wts) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  choose_row(z + (size_t)r * z_stride, E, top, mode, corr, lane, ids + (size_t)r * top, wts + (size_t)r * top);
 }
 
 
@@ -68,7 +93,8 @@ template <typename T, int R>
 __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ h, const float* __restrict__ w,
                                                          const float* __restrict__ b, float* __restrict__ z_out,
                                                          int z_stride, int rows, int width, int E, int n_out,
-                                                         int top, int* __restrict__ ids, float* __restrict__ wts) {
+                                                         int top, int mode, const float* __restrict__ corr,
+                                                         int* __restrict__ ids, float* __restrict__ wts) {
   extern __shared__ float rs[];        // h[R][width], z[R][n_out]
   float* h_s = rs;
   float* z_s = rs + (size_t)R * width;
@@ -117,34 +143,7 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ h
   __syncthreads();
   if (warp >= R || r0 + warp >= rows) return;
   const int r = r0 + warp;
-  const float* zr = z_s + warp * n_out;
-  float best[MAX_TOP];
-  int pick[MAX_TOP];
-  for (int k = 0; k < top; ++k) {
-    float v = -INFINITY;
-    int at = 0x7fffffff;
-    for (int e = lane; e < E; e += 32) {
-      bool taken = false;
-      for (int j = 0; j < k; ++j) taken |= pick[j] == e;
-      const float x = zr[e];
-      if (!taken && (x > v || (x == v && e < at) || at == 0x7fffffff)) v = x, at = e;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
-      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
-      if (oa != 0x7fffffff && (at == 0x7fffffff || ov > v || (ov == v && oa < at))) v = ov, at = oa;
-    }
-    best[k] = v, pick[k] = at;
-  }
-  if (lane == 0) {
-    float sum = 0.f;
-    for (int k = 0; k < top; ++k) sum += expf(best[k] - best[0]);
-    for (int k = 0; k < top; ++k) {
-      ids[(size_t)r * top + k] = pick[k];
-      wts[(size_t)r * top + k] = expf(best[k] - best[0]) / sum;
-    }
-  }
+  choose_row(z_s + warp * n_out, E, top, mode, corr, lane, ids + (size_t)r * top, wts + (size_t)r * top);
 }
 
 template <typename T> __device__ __forceinline__ float dot_row(const T* __restrict__ w, const float* __restrict__ x,
@@ -179,12 +178,14 @@ template <> __device__ __forceinline__ float dot_row<bf16>(const bf16* __restric
 template <typename T>
 __global__ void __launch_bounds__(128) moe_gate_up_rows_kernel(const T* __restrict__ h, const T* __restrict__ gate_up,
                                                                const int* __restrict__ ids, T* __restrict__ act,
-                                                               int width, int ff, int top) {
+                                                               int width, int ff, int top, int E, int kind,
+                                                               float limit) {
   extern __shared__ float h_s[];
   pdl_trigger();
   pdl_wait();
   const int item = blockIdx.x, r = item / top;
   const int e = ids[item];
+  if (e < 0 || e >= E) return;       // an identity expert: it has no matrices
   for (int i = threadIdx.x; i < width; i += blockDim.x) h_s[i] = to_f32(h[(size_t)r * width + i]);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -192,7 +193,16 @@ __global__ void __launch_bounds__(128) moe_gate_up_rows_kernel(const T* __restri
   for (int f = blockIdx.y * 8 + warp; f < min(ff, blockIdx.y * 8 + 8); f += 4) {
     const float g = dot_row<T>(we + (size_t)f * width, h_s, width, lane);
     const float u = dot_row<T>(we + (size_t)(ff + f) * width, h_s, width, lane);
-    if (lane == 0) act[(size_t)item * ff + f] = from_f32<T>(g / (1.f + expf(-g)) * u);
+    if (lane == 0) {
+      float y;
+      if (kind == 2) {       // the gate bounded above, the other half on both sides and one added to it
+        const float gc = fminf(g, limit), uc = fminf(fmaxf(u, -limit), limit);
+        y = gc / (1.f + expf(-1.702f * gc)) * (uc + 1.f);
+      } else {
+        y = g / (1.f + expf(-g)) * u;
+      }
+      act[(size_t)item * ff + f] = from_f32<T>(y);
+    }
   }
 }
 
@@ -203,19 +213,25 @@ __global__ void __launch_bounds__(128) moe_down_rows_kernel(const T* __restrict_
                                                             const int* __restrict__ ids, const float* __restrict__ wts,
                                                             float* __restrict__ shared, const float* __restrict__ gate,
                                                             int gate_stride, float* __restrict__ y, int width, int ff,
-                                                            int top, int accumulate, int clear_shared) {
+                                                            int top, int accumulate, int clear_shared, int E,
+                                                            const T* __restrict__ h) {
   extern __shared__ float a_s[];
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.x;
-  for (int i = threadIdx.x; i < top * ff; i += blockDim.x) a_s[i] = to_f32(act[(size_t)r * top * ff + i]);
+  for (int i = threadIdx.x; i < top * ff; i += blockDim.x) {
+    const int e = ids[(size_t)r * top + i / ff];
+    a_s[i] = e >= 0 && e < E ? to_f32(act[(size_t)r * top * ff + i]) : 0.f;
+  }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int c = blockIdx.y * 8 + warp; c < min(width, blockIdx.y * 8 + 8); c += 4) {
     float sum = 0.f;
     for (int k = 0; k < top; ++k) {
       const int e = ids[(size_t)r * top + k];
-      const float d = dot_row<T>(down + ((size_t)e * width + c) * ff, a_s + (size_t)k * ff, ff, lane);
+      // an expert behind the E with matrices is the identity: its output is the input itself
+      const float d = e >= 0 && e < E ? dot_row<T>(down + ((size_t)e * width + c) * ff, a_s + (size_t)k * ff, ff, lane)
+                                      : to_f32(h[(size_t)r * width + c]);
       sum = fmaf(wts[(size_t)r * top + k], d, sum);
     }
     if (lane == 0) {
@@ -265,10 +281,12 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__
 // xp[pos[i]][:] = h[i / top][:]
 template <typename T>
 __global__ void __launch_bounds__(128) moe_gather_kernel(const T* __restrict__ h, const int* __restrict__ pos,
-                                                         T* __restrict__ xp, int width, int top) {
+                                                         T* __restrict__ xp, int width, int top,
+                                                         const int* __restrict__ ids, int E) {
   pdl_trigger();
   pdl_wait();
   const int i = blockIdx.x;
+  if (ids && (ids[i] < 0 || ids[i] >= E)) return;      // an identity expert has no row in the buffer
   const T* src = h + (size_t)(i / top) * width;
   T* dst = xp + (size_t)pos[i] * width;
   if ((width * sizeof(T)) % 16 == 0 && (((uintptr_t)h | (uintptr_t)xp) & 15) == 0) {
@@ -286,15 +304,22 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
                                                           float* __restrict__ shared,
                                                           const float* __restrict__ gate, int gate_stride,
                                                           float* __restrict__ y, int width, int top, int accumulate,
-                                                          int clear_shared) {
+                                                          int clear_shared, const int* __restrict__ ids, int E,
+                                                          const void* __restrict__ x_id, int x_dtype, int x_stride) {
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.x;
   const float g = shared ? 1.f / (1.f + expf(-gate[(size_t)r * gate_stride])) : 0.f;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float sum = 0.f;
-    for (int k = 0; k < top; ++k)
-      sum = fmaf(wts[(size_t)r * top + k], d[(size_t)pos[(size_t)r * top + k] * width + c], sum);
+    for (int k = 0; k < top; ++k) {
+      // (with ids: an expert behind the E with matrices is the identity, its output the row of x_id)
+      const bool identity = ids && (ids[(size_t)r * top + k] < 0 || ids[(size_t)r * top + k] >= E);
+      const float v = !identity ? d[(size_t)pos[(size_t)r * top + k] * width + c]
+                      : x_dtype == LLM_BF16 ? to_f32(((const bf16*)x_id)[(size_t)r * x_stride + c])
+                                            : ((const float*)x_id)[(size_t)r * x_stride + c];
+      sum = fmaf(wts[(size_t)r * top + k], v, sum);
+    }
     if (shared) {
       sum = fmaf(g, shared[(size_t)r * width + c], sum);
       if (clear_shared) shared[(size_t)r * width + c] = 0.f;
@@ -313,30 +338,36 @@ LLM_EXPORT int llm_moe_align(const int* ids, int n_pairs, int E, int bn, int n_t
                     pos, tile_group);
 }
 
+// (ids with E: pairs whose expert is not one of the E with matrices are left out)
 LLM_EXPORT int llm_moe_gather(const void* h, const int* pos, void* xp, int dtype, int n_pairs, int width, int top,
-                              cudaStream_t stream) {
+                              const int* ids, int E, cudaStream_t stream) {
   if (n_pairs <= 0) return 0;
   if (dtype == LLM_F32)
-    return launch_pdl(moe_gather_kernel<float>, n_pairs, 128, 0, stream, (const float*)h, pos, (float*)xp, width, top);
+    return launch_pdl(moe_gather_kernel<float>, n_pairs, 128, 0, stream, (const float*)h, pos, (float*)xp, width, top,
+                      ids, E);
   if (dtype == LLM_BF16)
-    return launch_pdl(moe_gather_kernel<bf16>, n_pairs, 128, 0, stream, (const bf16*)h, pos, (bf16*)xp, width, top);
+    return launch_pdl(moe_gather_kernel<bf16>, n_pairs, 128, 0, stream, (const bf16*)h, pos, (bf16*)xp, width, top,
+                      ids, E);
   return LLM_ERR_UNSUPPORTED;
 }
 
 LLM_EXPORT int llm_moe_combine(const float* d, const int* pos, const float* wts, float* shared,
                                const float* gate, int gate_stride, float* y, int rows, int width, int top,
-                               int accumulate, int clear_shared, cudaStream_t stream) {
+                               int accumulate, int clear_shared, const int* ids, int E, const void* x_id,
+                               int x_dtype, int x_stride, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (shared && !gate) return LLM_ERR_ARGUMENT;
+  if ((shared && !gate) || (ids && !x_id)) return LLM_ERR_ARGUMENT;
   return launched_many_blocks(launch_pdl(moe_combine_kernel, rows, 256, 0, stream, d, pos, wts, shared, gate,
-                                         gate_stride, y, width, top, accumulate, clear_shared), rows);
+                                         gate_stride, y, width, top, accumulate, clear_shared, ids, E, x_id,
+                                         x_dtype, x_stride), rows);
 }
 
 // The router: z_out[r][0:n_out] = w h_r + b (w float32 [n_out][width], the first E rows the
 // experts'), ids / wts the `top` chosen experts of every row and their weights.
+// mode and corr: see choose_row.
 LLM_EXPORT int llm_moe_router(const void* h, int dtype, const float* w, const float* b, float* z_out, int z_stride,
-                              int rows, int width, int E, int n_out, int top, int* ids, float* wts,
-                              cudaStream_t stream) {
+                              int rows, int width, int E, int n_out, int top, int mode, const float* corr,
+                              int* ids, float* wts, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (top < 1 || top > MAX_TOP || top > E || n_out < E) return LLM_ERR_UNSUPPORTED;
   if ((size_t)(width + n_out) * 4 > 200 * 1024) return LLM_ERR_UNSUPPORTED;
@@ -350,7 +381,7 @@ LLM_EXPORT int llm_moe_router(const void* h, int dtype, const float* w, const fl
     if (smem > 48 * 1024)                                                                                      \
       cudaFuncSetAttribute(moe_router_kernel<T, RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
     return launch_pdl(moe_router_kernel<T, RR>, blocks, 256, smem, stream, (const T*)h, w, b, z_out, z_stride, \
-                      rows, width, E, n_out, top, ids, wts);                                                   \
+                      rows, width, E, n_out, top, mode, corr, ids, wts);                                       \
   } while (0)
   if (dtype == LLM_F32) {
     if (four) ROUTER(float, 4);
@@ -364,15 +395,19 @@ LLM_EXPORT int llm_moe_router(const void* h, int dtype, const float* w, const fl
   return LLM_ERR_UNSUPPORTED;
 }
 
-LLM_EXPORT int llm_moe_route(const float* z, int z_stride, int rows, int E, int top, int* ids, float* wts,
-                             cudaStream_t stream) {
+LLM_EXPORT int llm_moe_route(const float* z, int z_stride, int rows, int E, int top, int mode, const float* corr,
+                             int* ids, float* wts, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (top < 1 || top > MAX_TOP || top > E) return LLM_ERR_UNSUPPORTED;
-  return launch_pdl(moe_route_kernel, (rows + 3) / 4, 128, 0, stream, z, z_stride, rows, E, top, ids, wts);
+  if (top < 1 || top > MAX_TOP || top > E || mode < 0 || mode > 1) return LLM_ERR_UNSUPPORTED;
+  return launch_pdl(moe_route_kernel, (rows + 3) / 4, 128, 0, stream, z, z_stride, rows, E, top, mode, corr, ids,
+                    wts);
 }
 
+// E: experts with matrices (a pair whose expert is not one of them is left out); kind 0: silu(g) u,
+// 2: the clamped form with `limit` (see activations.cu)
 LLM_EXPORT int llm_moe_gate_up_rows(const void* h, const void* gate_up, const int* ids, void* act, int dtype,
-                                    int rows, int width, int ff, int top, cudaStream_t stream) {
+                                    int rows, int width, int ff, int top, int E, int kind, float limit,
+                                    cudaStream_t stream) {
   if (rows <= 0) return 0;
   if ((ff + 7) / 8 > 65535 || (size_t)width * 4 > 200 * 1024) return LLM_ERR_UNSUPPORTED;
   const dim3 grid(rows * top, (ff + 7) / 8);
@@ -381,13 +416,13 @@ LLM_EXPORT int llm_moe_gate_up_rows(const void* h, const void* gate_up, const in
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(moe_gate_up_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return launch_pdl(moe_gate_up_rows_kernel<float>, grid, 128, smem, stream, (const float*)h,
-                      (const float*)gate_up, ids, (float*)act, width, ff, top);
+                      (const float*)gate_up, ids, (float*)act, width, ff, top, E, kind, limit);
   }
   if (dtype == LLM_BF16) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(moe_gate_up_rows_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return launch_pdl(moe_gate_up_rows_kernel<bf16>, grid, 128, smem, stream, (const bf16*)h, (const bf16*)gate_up,
-                      ids, (bf16*)act, width, ff, top);
+                      ids, (bf16*)act, width, ff, top, E, kind, limit);
   }
   return LLM_ERR_UNSUPPORTED;
 }
@@ -395,7 +430,7 @@ LLM_EXPORT int llm_moe_gate_up_rows(const void* h, const void* gate_up, const in
 LLM_EXPORT int llm_moe_down_rows(const void* act, const void* down, const int* ids, const float* wts,
                                  float* shared, const float* gate, int gate_stride, float* y, int dtype,
                                  int rows, int width, int ff, int top, int accumulate, int clear_shared,
-                                 cudaStream_t stream) {
+                                 int E, const void* h, cudaStream_t stream) {
   if (rows <= 0) return 0;
   const size_t smem = (size_t)top * ff * 4;
   if ((width + 7) / 8 > 65535 || smem > 200 * 1024) return LLM_ERR_UNSUPPORTED;
@@ -405,13 +440,14 @@ LLM_EXPORT int llm_moe_down_rows(const void* act, const void* down, const int* i
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(moe_down_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return launch_pdl(moe_down_rows_kernel<float>, grid, 128, smem, stream, (const float*)act, (const float*)down,
-                      ids, wts, shared, gate, gate_stride, y, width, ff, top, accumulate, clear_shared);
+                      ids, wts, shared, gate, gate_stride, y, width, ff, top, accumulate, clear_shared, E,
+                      (const float*)h);
   }
   if (dtype == LLM_BF16) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(moe_down_rows_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return launch_pdl(moe_down_rows_kernel<bf16>, grid, 128, smem, stream, (const bf16*)act, (const bf16*)down, ids,
-                      wts, shared, gate, gate_stride, y, width, ff, top, accumulate, clear_shared);
+                      wts, shared, gate, gate_stride, y, width, ff, top, accumulate, clear_shared, E, (const bf16*)h);
   }
   return LLM_ERR_UNSUPPORTED;
 }

@@ -317,7 +317,8 @@ __global__ void causal_conv_silu_kernel(const float* __restrict__ src, int src_s
                                         const float* __restrict__ w, const float* __restrict__ b,
                                         const float* __restrict__ hist, long long hist_stride,
                                         const int* __restrict__ row_slot, const int* __restrict__ seg,
-                                        int single, float* __restrict__ out, int out_stride, int C, int taps) {
+                                        int single, float* __restrict__ out, int out_stride, int C, int taps,
+                                        int act) {
   pdl_trigger();
   pdl_wait();
   const int c = blockIdx.y * blockDim.x + threadIdx.x, r = blockIdx.x;
@@ -330,7 +331,7 @@ __global__ void causal_conv_silu_kernel(const float* __restrict__ src, int src_s
     const float x = j <= before ? src[(size_t)(r - j) * src_stride + c] : hrow[taps - 1 - (j - before)];
     acc = fmaf(w[(size_t)c * taps + taps - 1 - j], x, acc);
   }
-  out[(size_t)r * out_stride + c] = silu_f(acc);
+  out[(size_t)r * out_stride + c] = act ? silu_f(acc) : acc;
 }
 
 // The same for 2 to 4 taps with a thread walking a strip of rows of its channel: the weights and
@@ -342,7 +343,7 @@ __global__ void causal_conv_silu_strip_kernel(const float* __restrict__ src, int
                                               const float* __restrict__ hist, long long hist_stride,
                                               const int* __restrict__ row_slot, const int* __restrict__ seg,
                                               int single, float* __restrict__ out, int out_stride, int rows,
-                                              int C) {
+                                              int C, int act) {
   constexpr int R = 16;
   pdl_trigger();
   pdl_wait();
@@ -366,7 +367,7 @@ __global__ void causal_conv_silu_strip_kernel(const float* __restrict__ src, int
       acc = fmaf(wt[TAPS - 1 - j], x, acc);
     }
     acc = fmaf(wt[TAPS - 1], x0, acc);
-    out[(size_t)r * out_stride + c] = silu_f(acc);
+    out[(size_t)r * out_stride + c] = act ? silu_f(acc) : acc;
 #pragma unroll
     for (int j = TAPS - 1; j >= 1; --j) win[j] = win[j - 1];
     win[0] = x0;
@@ -693,28 +694,117 @@ LLM_EXPORT int llm_bias_sigmoid_pow(float* z, const float* b, int rows, int n, f
 
 // The convolution of `C` channels over the rows of a step, then the request's history of inputs
 // brought up to date (two launches: the second overwrites what the first reads).
-LLM_EXPORT int llm_causal_conv_silu(const float* src, int src_stride, const float* w, const float* b,
-                                    float* hist, long long hist_stride, const int* row_slot, const int* seg,
-                                    int rows, int n_slots, int single, float* out, int out_stride, int C,
-                                    int taps, cudaStream_t stream) {
+// (act 1: silu behind the sum, 0: the sum as it is)
+LLM_EXPORT int llm_causal_conv(const float* src, int src_stride, const float* w, const float* b,
+                               float* hist, long long hist_stride, const int* row_slot, const int* seg,
+                               int rows, int n_slots, int single, float* out, int out_stride, int C,
+                               int taps, int act, cudaStream_t stream) {
   if (rows <= 0 || C <= 0) return 0;
   if (taps < 1 || (!single && !seg)) return LLM_ERR_ARGUMENT;
   int rc;
   const dim3 strips((rows + 15) / 16, (C + 127) / 128);
 #define STRIP(T)                                                                                             \
   rc = launch_pdl(causal_conv_silu_strip_kernel<T>, strips, 128, 0, stream, src, src_stride, w, b,            \
-                  (const float*)hist, hist_stride, row_slot, seg, single, out, out_stride, rows, C)
+                  (const float*)hist, hist_stride, row_slot, seg, single, out, out_stride, rows, C, act)
   // (strips pay from a few hundred rows on; a decode step has too few rows to fill the GPU with them)
   if (taps == 2 && rows >= 256) STRIP(2);
   else if (taps == 3 && rows >= 256) STRIP(3);
   else if (taps == 4 && rows >= 256) STRIP(4);
   else
     rc = launch_pdl(causal_conv_silu_kernel, dim3(rows, (C + 127) / 128), 128, 0, stream, src, src_stride, w, b,
-                    (const float*)hist, hist_stride, row_slot, seg, single, out, out_stride, C, taps);
+                    (const float*)hist, hist_stride, row_slot, seg, single, out, out_stride, C, taps, act);
 #undef STRIP
   if (rc != 0 || taps == 1) return rc;
   return launch_pdl(conv_history_kernel, dim3(single ? rows : n_slots, (C + 127) / 128), 128, 0, stream, src,
                     src_stride, hist, hist_stride, row_slot, seg, single, C, taps);
+}
+
+LLM_EXPORT int llm_causal_conv_silu(const float* src, int src_stride, const float* w, const float* b,
+                                    float* hist, long long hist_stride, const int* row_slot, const int* seg,
+                                    int rows, int n_slots, int single, float* out, int out_stride, int C,
+                                    int taps, cudaStream_t stream) {
+  return llm_causal_conv(src, src_stride, w, b, hist, hist_stride, row_slot, seg, rows, n_slots, single, out,
+                         out_stride, C, taps, 1, stream);
+}
+
+// ---- minGRU: a gated recurrence per channel whose gates read only the current token
+//   z = sigmoid(zr + bz), u = ur + bx, candidate c = u + 1/2 (u >= 0) or sigmoid(u) (u < 0)
+//   S <- (1 - z) S + z c;  out = S * silu(g)                              (all 32-bit)
+// Two passes.  The first is elementwise over the step: it overwrites zr with the weight 1 - z
+// of the old state, ur with z c and g with silu(g).  The second walks every request's rows in
+// order, a thread per (request, channel), with one multiply-add per token in the chain; the
+// state is carried through memory unrounded, so a row's result does not depend on how the
+// tokens were cut into steps.
+__global__ void min_gru_gates_kernel(float* __restrict__ z, float* __restrict__ u, float* __restrict__ g,
+                                     int stride, const float* __restrict__ bz, const float* __restrict__ bx,
+                                     long long total, int width) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / width;
+    const int c = (int)(i - r * width);
+    const size_t at = (size_t)r * stride + c;
+    const float zz = 1.f / (1.f + expf(-(z[at] + (bz ? bz[c] : 0.f))));
+    const float uu = u[at] + (bx ? bx[c] : 0.f);
+    const float cand = uu >= 0.f ? uu + 0.5f : 1.f / (1.f + expf(-uu));
+    z[at] = 1.f - zz;
+    u[at] = zz * cand;
+    g[at] = silu_f(g[at]);
+  }
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(128) min_gru_scan_kernel(const float* __restrict__ keep, const float* __restrict__ add,
+                                                           const float* __restrict__ gate, int stride,
+                                                           float* __restrict__ state, long long state_stride,
+                                                           TOut* __restrict__ out, int out_stride,
+                                                           const int* __restrict__ row_slot,
+                                                           const int* __restrict__ seg, int single, int width) {
+  pdl_trigger();
+  pdl_wait();
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= width) return;
+  int slot, first, end;
+  if (single) {
+    first = blockIdx.x, end = first + 1, slot = row_slot[first];
+  } else {
+    slot = blockIdx.x;
+    first = seg[SEG * slot], end = seg[SEG * slot + 1];
+  }
+  if (end <= first) return;
+  float* sp = state + (size_t)slot * state_stride + c;
+  float S = *sp;
+  for (int r = first; r < end; ++r) {
+    const size_t at = (size_t)r * stride + c;
+    S = fmaf(keep[at], S, add[at]);
+    out[(size_t)r * out_stride + c] = from_f32<TOut>(S * gate[at]);
+  }
+  *sp = S;
+}
+
+// z, u, g: three column ranges of one float32 matrix of row stride `stride` (overwritten);
+// state float32 [slots][>= width]; out [rows][width] in out_dtype.
+LLM_EXPORT int llm_min_gru(float* z, float* u, float* g, int stride, const float* bz, const float* bx,
+                           float* state, long long state_stride, void* out, int out_dtype, int out_stride,
+                           const int* row_slot, const int* seg, int rows, int n_slots, int single, int width,
+                           cudaStream_t stream) {
+  if (rows <= 0 || width <= 0) return 0;
+  if (!single && !seg) return LLM_ERR_ARGUMENT;
+  const long long total = (long long)rows * width;
+  const int blocks = (int)((total + 255) / 256 < 2368 ? (total + 255) / 256 : 2368);
+  int rc = launch_pdl(min_gru_gates_kernel, blocks, 256, 0, stream, z, u, g, stride, bz, bx, total, width);
+  if (rc) return rc;
+  const dim3 grid(single ? rows : n_slots, (width + 127) / 128);
+  if (out_dtype == LLM_F32)
+    return launch_pdl(min_gru_scan_kernel<float>, grid, 128, 0, stream, (const float*)z, (const float*)u,
+                      (const float*)g, stride, state, state_stride, (float*)out, out_stride, row_slot, seg, single,
+                      width);
+  if (out_dtype == LLM_BF16)
+    return launch_pdl(min_gru_scan_kernel<bf16>, grid, 128, 0, stream, (const float*)z, (const float*)u,
+                      (const float*)g, stride, state, state_stride, (bf16*)out, out_stride, row_slot, seg, single,
+                      width);
+  return LLM_ERR_UNSUPPORTED;
 }
 
 LLM_EXPORT int llm_gated_group_norm(const float* o, int o_stride, const float* x, int x_stride,

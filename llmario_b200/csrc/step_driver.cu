@@ -47,6 +47,12 @@ int llm_qk_norm_rope_store(const float* proj, int proj_stride, void* q_out, void
                            float eps, int has_kv, int use_norm, int clear_proj, cudaStream_t stream);
 int llm_rope_table(const int* row_pos, const float* inv_freq, float* cos_sin, int rows, int half,
                    float attn_factor, cudaStream_t stream);
+int llm_attention_generic_ext(const void* q, void* out, const void* k_cache, const void* v_cache, int dtype,
+                              long long page_stride, const int* block_table, int table_stride, const int* row_slot,
+                              const int* row_pos, int rows, int Hq, int Hkv, int hd, int page_size, float scale,
+                              int window, const float* sink, int vd, int keep_first, const void* pk_cache,
+                              const void* pv_cache, long long p_page_stride, const int* p_table, int p_table_stride,
+                              int pool, cudaStream_t stream);
 int llm_attention_generic(const void* q, void* out, const void* k_cache, const void* v_cache, int dtype,
                           long long page_stride, const int* block_table, int table_stride,
                           const int* row_slot, const int* row_pos, int rows, int Hq, int Hkv, int hd,
@@ -519,6 +525,14 @@ struct Run {
     const bool whole_values = L.value_dim == 0 || L.value_dim == hd;
     const int ps = c.page_size;
     const bool tc = (hd == 64 || hd == 128) && 128 % group == 0 && (c.page_stride * 2) % 16 == 0;
+    // kept first keys and pooled blocks make a row's visible keys more than one range: the
+    // generic kernel walks them, the others know one range
+    if (L.keep_first > 0 || L.pool > 0)
+      return check(llm_attention_generic_ext(q, out, c.k, c.v, st.dtype, c.page_stride, c.block_table,
+                                             c.table_stride, st.row_slot, st.row_pos, st.rows, Hq, Hkv, hd,
+                                             c.page_size, L.scale, window, L.sink, L.value_dim, L.keep_first,
+                                             L.pool > 0 ? L.pool_k : nullptr, L.pool_v, L.pool_page_stride,
+                                             L.pool_table, L.pool_table_stride, L.pool, stream), K_GENERIC);
     if (!whole_values || st.dtype != LLM_BF16 || !(hd == 32 || hd == 64 || hd == 128) || group > 16 ||
         (L.sink != nullptr && !tc))
       return check(llm_attention_generic(q, out, c.k, c.v, st.dtype, c.page_stride, c.block_table,

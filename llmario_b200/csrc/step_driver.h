@@ -30,6 +30,14 @@ struct LlmLayerDesc {
   const void* w_gate_up;   // [2 * intermediate][hidden]
   const void* w_down;      // [hidden][intermediate]
   const float* sink;       // null, or a number per query head added to the softmax's sum as exp(sink)
+  int keep_first;          // with a window: the first so many keys of a sequence are seen as well
+  int pool;                // > 0 (with a window): the blocks of so many positions that lie wholly behind the
+                           // window are seen through a second cache with one key and value per block
+  const void* pool_k;      // that cache: K and V planes of page 0, its block table
+  const void* pool_v;
+  const int* pool_table;
+  long long pool_page_stride;
+  int pool_table_stride, pad2_;
 };
 
 // One run-order entry: which layer, and where its keys and values live.

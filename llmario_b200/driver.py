@@ -32,7 +32,9 @@ class LayerDesc(Structure):
                 ("mixer_norm_w", c_void_p), ("ffn_norm_w", c_void_p), ("q_norm_w", c_void_p),
                 ("k_norm_w", c_void_p), ("inv_freq", c_void_p), ("w_qkv", c_void_p),
                 ("w_o", c_void_p), ("w_gate_up", c_void_p), ("w_down", c_void_p),
-                ("sink", c_void_p)]
+                ("sink", c_void_p), ("keep_first", c_int), ("pool", c_int), ("pool_k", c_void_p),
+                ("pool_v", c_void_p), ("pool_table", c_void_p), ("pool_page_stride", c_longlong),
+                ("pool_table_stride", c_int), ("pad2_", c_int)]
 
 
 class CallDesc(Structure):
@@ -200,7 +202,8 @@ def tensor_core_attention(dtype: torch.dtype, view, num_heads: int, num_kv_heads
 
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num_kv_heads: int,
               head_dim: int, scale: float, window: Optional[int],
-              sink: Optional[torch.Tensor] = None, value_dim: Optional[int] = None) -> None:
+              sink: Optional[torch.Tensor] = None, value_dim: Optional[int] = None,
+              keep_first: int = 0, pool: int = 0, pooled_view=None) -> None:
     """(``window``: None or 0 for every earlier key, a positive number for the last so many, a
     negative one for the query's own chunk of that many positions: ``kernels.mask_code``.)
     Causal attention of every row of the step over its own request's cached keys, by the
@@ -210,13 +213,28 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, view, num_heads: int, num
     portions read a gathered copy of their keys); everything else (32-bit, other head sizes,
     very large groups) to the generic kernel.  ``sink`` (float32, one number per query head)
     joins the softmax's sum as ``exp(sink)`` without a value; ``value_dim`` says that only the
-    first so many channels of a value row count (``out`` is then ``[rows, heads * value_dim]``)."""
+    first so many channels of a value row count (``out`` is then ``[rows, heads * value_dim]``).
+    ``keep_first`` (with a window): the first so many keys of a sequence are seen from every
+    later position.  ``pool`` with ``pooled_view`` (with a window): the view of a second cache
+    that holds one key and value per block of ``pool`` positions; a row sees the blocks that
+    lie wholly behind its window, in the same softmax."""
     kernels._cuda(q, out, view.k, view.v, view.block_table)
     assert q.dtype == out.dtype and q.is_contiguous() and out.is_contiguous()
     layer = LayerDesc()
     layer.num_heads, layer.num_kv_heads, layer.head_dim = num_heads, num_kv_heads, head_dim
     layer.scale, layer.window = scale, int(window or 0)
     layer.value_dim = int(value_dim or 0)
+    layer.keep_first = int(keep_first or 0)
+    if pool:
+        if pooled_view is None or not layer.window > 0 or pooled_view.page_size != view.page_size:
+            raise kernels.KernelError("pooled blocks need their cache (pages of the same size) "
+                                      "and a window")
+        kernels._cuda(pooled_view.k, pooled_view.v, pooled_view.block_table)
+        layer.pool = int(pool)
+        layer.pool_k, layer.pool_v = pooled_view.k.data_ptr(), pooled_view.v.data_ptr()
+        layer.pool_table = pooled_view.block_table.data_ptr()
+        layer.pool_page_stride = pooled_view.page_stride
+        layer.pool_table_stride = pooled_view.block_table.stride(0)
     if sink is not None:
         kernels._cuda(sink)
         assert sink.dtype == torch.float32 and sink.numel() == num_heads

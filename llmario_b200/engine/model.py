@@ -12,6 +12,7 @@ import torch
 
 from ..config import ModelSpec, load_spec
 from ..parts import BoundCall, build_part, graph_safe, part_class, streamed_weights_of
+from ..parts.base import cache_needs_of
 from ..weights import check_tensors, load_weights, random_tensors
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
@@ -65,7 +66,7 @@ class Model:
         for i, call in enumerate(spec.run_order):
             block = self.blocks[call.layer]
             mine = list(block.cache_needs()) if hasattr(block, "cache_needs") \
-                else [block.mixer.cache_need()]
+                else cache_needs_of(block.mixer)
             start = len(self._needs)
             self._needs += mine
             if call.reads_cache_of is None:

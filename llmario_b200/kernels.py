@@ -52,6 +52,16 @@ def _signatures():
                                    I, F, I, I, I, P],
         "llm_rope_table": [P, P, P, I, I, F, P],
         "llm_attention_generic": [P, P, P, P, I, L, P, I, P, P, I, I, I, I, I, F, I, P, I, P],
+        "llm_attention_generic_ext": [P, P, P, P, I, L, P, I, P, P, I, I, I, I, I, F, I, P, I, I, P,
+                                      P, L, P, I, I, P],
+        "llm_qkv_store": [P, I, P, I, P, I, P, P, P, P, P, P, I, L, P, I, P, P, I, I, I, I, I, I, I,
+                          I, F, I, I, P],
+        "llm_pool_blocks": [P, P, L, P, I, P, P, L, P, I, P, P, I, I, I, I, I, I, P],
+        "llm_causal_conv": [P, I, P, P, P, L, P, P, I, I, I, P, I, I, I, I, P],
+        "llm_min_gru": [P, P, P, I, P, P, P, L, P, I, I, P, P, I, I, I, I, P],
+        "llm_gated_act_limit": [P, P, P, I, I, I, I, I, F, P],
+        "llm_act_rows": [P, P, I, L, I, I, P],
+        "llm_dual_norm_mean": [P, P, P, P, P, I, I, F, I, P],
         "llm_sample": [P, L, I, I, P, P, P, P, P, P, P, P, P],
         "llm_gemv_bf16": [P, P, P, I, I, I, I, I, I, I, I, I, P],
         "llm_gemm_tcgen05": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, P],
@@ -88,15 +98,15 @@ def _signatures():
         "llm_latent_store": [P, I, P, P, P, I, P, P, P, I, L, P, I, P, P, I, I, I, I, I, F, I, I, P],
         "llm_latent_query": [P, I, P, I, P, P, I, I, I, I, I, I, I, P],
         "llm_gemm_simt_batched": [P, P, P, I, I, I, I, I, I, I, I, I, L, L, L, P],
-        "llm_moe_route": [P, I, I, I, I, P, P, P],
-        "llm_moe_router": [P, I, P, P, P, I, I, I, I, I, I, P, P, P],
+        "llm_moe_route": [P, I, I, I, I, I, P, P, P, P],
+        "llm_moe_router": [P, I, P, P, P, I, I, I, I, I, I, I, P, P, P, P],
         "llm_moe_align": [P, I, I, I, I, P, P, P],
-        "llm_moe_gather": [P, P, P, I, I, I, I, P],
-        "llm_moe_combine": [P, P, P, P, P, I, P, I, I, I, I, I, P],
+        "llm_moe_gather": [P, P, P, I, I, I, I, P, I, P],
+        "llm_moe_combine": [P, P, P, P, P, I, P, I, I, I, I, I, P, I, P, I, I, P],
         "llm_gemm_tcgen05_grouped": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P, P],
         "llm_gemm_tcgen05_batched": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P],
-        "llm_moe_gate_up_rows": [P, P, P, P, I, I, I, I, I, P],
-        "llm_moe_down_rows": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, P],
+        "llm_moe_gate_up_rows": [P, P, P, P, I, I, I, I, I, I, I, F, P],
+        "llm_moe_down_rows": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, P, P],
         "llm_causal_conv_silu": [P, I, P, P, P, L, P, P, I, I, I, P, I, I, I, P],
         "llm_gated_group_norm": [P, I, P, I, P, I, P, I, P, I, P, I, I, I, I, I, F, I, P],
     }
@@ -472,12 +482,12 @@ def bias_sigmoid_pow(z: torch.Tensor, bias: Optional[torch.Tensor], exponent: fl
 
 def causal_conv_silu(src: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
                      history: torch.Tensor, out: torch.Tensor, row_slot: torch.Tensor,
-                     seg: Optional[torch.Tensor]) -> None:
+                     seg: Optional[torch.Tensor], activation: bool = True) -> None:
     """out[r, c] = silu(bias[c] + sum_j weight[c, taps-1-j] * input(r - j, c)) over each
     request's own tokens; inputs before the step come from ``history`` (float32
     [slots, >= channels * (taps - 1)], each channel's last taps - 1 inputs, oldest first), which
     is brought up to date afterwards.  src, out float32 [rows, channels] (column slices are
-    fine); weight float32 [channels, taps]."""
+    fine); weight float32 [channels, taps].  ``activation=False``: the sum as it is, no silu."""
     _cuda(src, weight, bias, history, out, row_slot, seg)
     for t in (src, weight, history, out):
         assert t.dtype == torch.float32 and t.stride(-1) == 1
@@ -485,10 +495,10 @@ def causal_conv_silu(src: torch.Tensor, weight: torch.Tensor, bias: Optional[tor
     taps = weight.shape[1]
     assert weight.is_contiguous() and weight.shape[0] == channels and src.shape == out.shape
     assert history.shape[1] >= channels * (taps - 1)
-    _check(lib().llm_causal_conv_silu(
+    _check(lib().llm_causal_conv(
         _ptr(src), src.stride(0), _ptr(weight), _ptr(bias), _ptr(history), history.stride(0),
         _ptr(row_slot), _ptr(seg), rows, history.shape[0], int(seg is None), _ptr(out),
-        out.stride(0), channels, taps, _stream()), "causal_conv_silu")
+        out.stride(0), channels, taps, int(activation), _stream()), "causal_conv")
     global launches
     launches += int(taps > 1)      # the history is brought up to date by a launch of its own
 
@@ -512,6 +522,83 @@ def gated_group_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor,
         _ptr(skip), head, _ptr(gate), gate.stride(0), _ptr(weight), weight.numel(), _ptr(out),
         _dt(out), out.stride(0), rows, channels // group, group, float(eps), int(gate_first),
         _stream()), "gated_group_norm")
+
+
+def min_gru(z: torch.Tensor, u: torch.Tensor, g: torch.Tensor, z_bias: Optional[torch.Tensor],
+            u_bias: Optional[torch.Tensor], state: torch.Tensor, out: torch.Tensor,
+            row_slot: torch.Tensor, seg: Optional[torch.Tensor]) -> None:
+    """Per request and channel ``S <- (1 - s) S + s c`` over the rows of the step in order, with
+    ``s = sigmoid(z + z_bias)`` and the candidate ``c = w + 1/2`` where ``w = u + u_bias >= 0``,
+    ``sigmoid(w)`` elsewhere; ``out = S * silu(g)``.  z, u, g: float32 column ranges of one
+    matrix (equal row strides; they are overwritten); state float32 [slots, >= channels],
+    carried from step to step; out [rows, channels].  ``seg``: the table of
+    :func:`segment_table`, or None when every row is a request of its own."""
+    _cuda(z, u, g, z_bias, u_bias, state, out, row_slot, seg)
+    for t in (z, u, g, state):
+        assert t.dtype == torch.float32 and t.stride(-1) == 1
+    rows, width = out.shape
+    assert z.shape == u.shape == g.shape == (rows, width) and out.stride(1) == 1
+    assert z.stride(0) == u.stride(0) == g.stride(0) and state.shape[1] >= width
+    for b in (z_bias, u_bias):
+        assert b is None or (b.dtype == torch.float32 and b.numel() == width)
+    _check(lib().llm_min_gru(_ptr(z), _ptr(u), _ptr(g), z.stride(0), _ptr(z_bias), _ptr(u_bias),
+                             _ptr(state), state.stride(0), _ptr(out), _dt(out), out.stride(0),
+                             _ptr(row_slot), _ptr(seg), rows, state.shape[0], int(seg is None),
+                             width, _stream()), "min_gru")
+    global launches
+    launches += 1          # the gates are a launch of their own
+
+
+NORM_NONE, NORM_PER_HEAD, NORM_WHOLE_ROW = 0, 1, 2
+
+
+def qkv_store(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor],
+              q_out: torch.Tensor, view, row_slot: torch.Tensor, row_pos: torch.Tensor,
+              num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, head_dim: int,
+              norm: int, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+              eps: float, rot_dim: int = 0, cos_sin: Optional[torch.Tensor] = None) -> None:
+    """Norm, rotation and stores for the rows of a step.  q float32 [rows, heads * key_dim],
+    k [rows, kv_heads * key_dim], v [rows, kv_heads * value_dim] (column slices are fine; k and
+    v None: only the queries).  ``norm``: NORM_NONE, NORM_PER_HEAD (weights [key_dim], shared by
+    the heads) or NORM_WHOLE_ROW (weights of the whole q and k rows).  ``rot_dim`` > 0: the
+    pairs (2i, 2i + 1) of every q and k head are turned by ``cos_sin`` (float32
+    [rows, rot_dim / 2, 2]).  q goes to ``q_out`` [rows, heads * head_dim], k and v into the
+    pages of ``view``; ``head_dim`` >= both sizes is the cache's row, padded with zeros."""
+    _cuda(q, k, v, q_out, q_weight, k_weight, cos_sin, row_slot, row_pos)
+    rows = q.shape[0]
+    has_kv = k is not None
+    for t in (q, k, v):
+        assert t is None or (t.dtype == torch.float32 and t.stride(1) == 1)
+    assert q_out.is_contiguous() and q_out.shape == (rows, num_heads * head_dim)
+    assert not has_kv or view.k.dtype == q_out.dtype
+    if rot_dim:
+        assert cos_sin is not None and cos_sin.dtype == torch.float32 and cos_sin.is_contiguous()
+        assert cos_sin.shape == (rows, rot_dim // 2, 2)
+    for w, n in ((q_weight, num_heads), (k_weight, num_kv_heads)):
+        if norm != NORM_NONE and w is not None:
+            assert w.dtype == torch.float32 and w.is_contiguous()
+            assert w.numel() == (key_dim if norm == NORM_PER_HEAD else n * key_dim)
+    _check(lib().llm_qkv_store(
+        _ptr(q), q.stride(0), _ptr(k), k.stride(0) if has_kv else 0, _ptr(v),
+        v.stride(0) if has_kv else 0, _ptr(q_weight), _ptr(k_weight), _ptr(cos_sin), _ptr(q_out),
+        _ptr(view.k) if has_kv else None, _ptr(view.v) if has_kv else None, _dt(q_out),
+        view.page_stride, _ptr(view.block_table), view.block_table.stride(0), _ptr(row_slot),
+        _ptr(row_pos), rows, num_heads, num_kv_heads, key_dim, value_dim, head_dim, rot_dim, norm,
+        float(eps), view.page_size, int(has_kv), _stream()), "qkv_store")
+
+
+def pool_blocks(view, pooled_view, row_slot: torch.Tensor, row_pos: torch.Tensor, rows: int,
+                num_kv_heads: int, head_dim: int, pool: int) -> None:
+    """Every row of the step whose position ends a block of ``pool`` tokens writes the block's
+    entry of the pooled cache: the means of its cached keys and of its cached values."""
+    _cuda(view.k, view.v, pooled_view.k, pooled_view.v, row_slot, row_pos)
+    assert view.page_size == pooled_view.page_size and view.k.dtype == pooled_view.k.dtype
+    _check(lib().llm_pool_blocks(
+        _ptr(view.k), _ptr(view.v), view.page_stride, _ptr(view.block_table),
+        view.block_table.stride(0), _ptr(pooled_view.k), _ptr(pooled_view.v),
+        pooled_view.page_stride, _ptr(pooled_view.block_table), pooled_view.block_table.stride(0),
+        _ptr(row_slot), _ptr(row_pos), _dt(view.k), rows, num_kv_heads, head_dim, view.page_size,
+        pool, _stream()), "pool_blocks")
 
 
 def random_normal(out: torch.Tensor, key: int, mean: float, std: float, first: int = 0) -> None:
@@ -1073,20 +1160,47 @@ def stream_fill(xs: torch.Tensor) -> None:
            "stream_fill")
 
 
-ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
+PLAIN_ACTIVATIONS = {"relu_squared": 3}
 
 
 def gated_act(gate_up: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-              activation: str, clear: bool = False) -> None:
+              activation: str, clear: bool = False, limit: float = 0.0) -> None:
     """out[t][j] = act(gate_up[t][j] + bias[j]) * (gate_up[t][ff + j] + bias[ff + j]).
-    ``clear``: gate_up is zeroed once read (a buffer that is kept at zero between steps)."""
+    ``clear``: gate_up is zeroed once read (a buffer that is kept at zero between steps).
+    ``clamped_swish`` with ``limit`` L: with g = min(gate, L) and u = clamp(up, -L, L) the result
+    is g * sigmoid(1.702 g) * (u + 1)."""
     _cuda(gate_up, bias, out)
     rows, ff = out.shape
     assert gate_up.dtype == torch.float32 and gate_up.is_contiguous() and out.is_contiguous()
     assert gate_up.shape == (rows, 2 * ff)
     assert bias is None or (bias.dtype == torch.float32 and bias.numel() == 2 * ff)
-    _check(lib().llm_gated_act(_ptr(gate_up), _ptr(bias), _ptr(out), _dt(out), rows, ff,
-                               ACTIVATIONS[activation], int(clear), _stream()), "gated_act")
+    _check(lib().llm_gated_act_limit(_ptr(gate_up), _ptr(bias), _ptr(out), _dt(out), rows, ff,
+                                     ACTIVATIONS[activation], int(clear), float(limit),
+                                     _stream()), "gated_act")
+
+
+def act_rows(x: torch.Tensor, out: torch.Tensor, activation: str, clear: bool = False) -> None:
+    """out = act(x) for an activation without a gate (``relu_squared``: max(x, 0)^2); x float32,
+    both contiguous and of one shape.  ``clear``: x is zeroed once read."""
+    _cuda(x, out)
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+    assert x.shape == out.shape
+    _check(lib().llm_act_rows(_ptr(x), _ptr(out), _dt(out), x.numel(),
+                              PLAIN_ACTIVATIONS[activation], int(clear), _stream()), "act_rows")
+
+
+def dual_norm_mean(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor,
+                   y: torch.Tensor, eps: float, accumulate: bool = False) -> None:
+    """y (=|+=) (unit(a) * wa + unit(b) * wb) / 2 row by row, unit(.) a row over its root mean square
+    (eps inside the root); all float32, [rows, width]."""
+    _cuda(a, b, wa, wb, y)
+    for t in (a, b, wa, wb, y):
+        assert t.dtype == torch.float32 and t.is_contiguous()
+    rows, width = y.shape
+    assert a.shape == b.shape == y.shape and wa.numel() == wb.numel() == width
+    _check(lib().llm_dual_norm_mean(_ptr(a), _ptr(b), _ptr(wa), _ptr(wb), _ptr(y), rows, width,
+                                    float(eps), int(accumulate), _stream()), "dual_norm_mean")
 
 
 def scale_soft_cap(z: torch.Tensor, scale: float, cap: float) -> None:
@@ -1162,25 +1276,44 @@ def head_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
                                        out.stride(1), _stream()), "head_linear")
 
 
-def moe_route(z: torch.Tensor, experts: int, top: int, ids: torch.Tensor, wts: torch.Tensor
-              ) -> None:
+ROUTE_SOFTMAX_CHOSEN, ROUTE_SOFTMAX_ALL = 0, 1
+
+
+def _route_mode(scores: str, correction: Optional[torch.Tensor], experts: int) -> int:
+    if scores not in ("softmax_chosen", "softmax_all"):
+        raise KernelError(f"router scores '{scores}' (softmax_chosen or softmax_all)")
+    if correction is not None:
+        assert scores == "softmax_all" and correction.dtype == torch.float32
+        assert correction.is_contiguous() and correction.numel() == experts
+    return ROUTE_SOFTMAX_ALL if scores == "softmax_all" else ROUTE_SOFTMAX_CHOSEN
+
+
+def moe_route(z: torch.Tensor, experts: int, top: int, ids: torch.Tensor, wts: torch.Tensor,
+              scores: str = "softmax_chosen", correction: Optional[torch.Tensor] = None) -> None:
     """Per row the ``top`` largest of the first ``experts`` logits of z (float32, a column slice
-    is fine) into ``ids`` (int32 [rows, top]) and the softmax over the chosen into ``wts``."""
-    _cuda(z, ids, wts)
+    is fine) into ``ids`` (int32 [rows, top]) and the softmax over the chosen into ``wts``.
+    ``scores="softmax_all"``: the scores are the softmax over all ``experts`` logits, the choice
+    goes by score + ``correction`` (float32 [experts], optional), and a chosen expert's weight is
+    its score, not renormalised."""
+    _cuda(z, ids, wts, correction)
+    mode = _route_mode(scores, correction, experts)
     rows = z.shape[0]
     assert z.dtype == torch.float32 and z.stride(1) == 1 and z.shape[1] >= experts
     assert ids.dtype == torch.int32 and ids.is_contiguous() and ids.shape == (rows, top)
     assert wts.dtype == torch.float32 and wts.is_contiguous() and wts.shape == (rows, top)
-    _check(lib().llm_moe_route(_ptr(z), z.stride(0), rows, experts, top, _ptr(ids), _ptr(wts),
-                               _stream()), "moe_route")
+    _check(lib().llm_moe_route(_ptr(z), z.stride(0), rows, experts, top, mode, _ptr(correction),
+                               _ptr(ids), _ptr(wts), _stream()), "moe_route")
 
 
 def moe_router(h: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], experts: int,
-               top: int, z: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor) -> None:
+               top: int, z: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor,
+               scores: str = "softmax_chosen", correction: Optional[torch.Tensor] = None) -> None:
     """Router logits ``z = h w^T + bias`` (w float32 [n_out, width], sums in 32-bit) and, over
     the first ``experts`` of them, the ``top`` largest per row into ``ids`` with the softmax over
-    the chosen into ``wts``: the product and :func:`moe_route` in one launch."""
-    _cuda(h, w, bias, z, ids, wts)
+    the chosen into ``wts``: the product and :func:`moe_route` in one launch (``scores`` and
+    ``correction`` as there)."""
+    _cuda(h, w, bias, z, ids, wts, correction)
+    mode = _route_mode(scores, correction, experts)
     rows, width = h.shape
     n_out = w.shape[0]
     assert w.dtype == torch.float32 and w.is_contiguous() and w.shape[1] == width
@@ -1189,29 +1322,40 @@ def moe_router(h: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], e
     assert ids.dtype == torch.int32 and ids.is_contiguous() and ids.shape == (rows, top)
     assert wts.dtype == torch.float32 and wts.is_contiguous() and wts.shape == (rows, top)
     _check(lib().llm_moe_router(_ptr(h), _dt(h), _ptr(w), _ptr(bias), _ptr(z), z.stride(0), rows,
-                                width, experts, n_out, top, _ptr(ids), _ptr(wts), _stream()),
+                                width, experts, n_out, top, mode, _ptr(correction), _ptr(ids),
+                                _ptr(wts), _stream()),
            "moe_router")
 
 
 def moe_gate_up_rows(h: torch.Tensor, gate_up: torch.Tensor, ids: torch.Tensor,
-                     act: torch.Tensor) -> None:
-    """act[r, k] = silu(Wg_e h_r) * (Wu_e h_r), e = ids[r, k]; gate_up [E, 2 ff, width]."""
+                     act: torch.Tensor, activation: str = "silu", limit: float = 0.0) -> None:
+    """act[r, k] = silu(Wg_e h_r) * (Wu_e h_r), e = ids[r, k]; gate_up [E, 2 ff, width].  With
+    ``activation="clamped_swish"`` the gated form of that name (see :func:`gated_act`).  A pair
+    whose expert is not one of the E with matrices is left out."""
     _cuda(h, gate_up, ids, act)
+    if activation not in ("silu", "clamped_swish"):
+        raise KernelError(f"routed experts have no activation '{activation}'")
     rows, width = h.shape
     top = ids.shape[1]
     ff = gate_up.shape[1] // 2
     assert h.is_contiguous() and gate_up.is_contiguous() and act.is_contiguous()
     assert h.dtype == gate_up.dtype == act.dtype and act.shape == (rows, top, ff)
     _check(lib().llm_moe_gate_up_rows(_ptr(h), _ptr(gate_up), _ptr(ids), _ptr(act), _dt(h), rows,
-                                      width, ff, top, _stream()), "moe_gate_up_rows")
+                                      width, ff, top, gate_up.shape[0], ACTIVATIONS[activation],
+                                      float(limit), _stream()), "moe_gate_up_rows")
 
 
 def moe_down_rows(act: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor,
                   y: torch.Tensor, accumulate: bool, shared: Optional[torch.Tensor] = None,
-                  shared_gate: Optional[torch.Tensor] = None, clear_shared: bool = False) -> None:
+                  shared_gate: Optional[torch.Tensor] = None, clear_shared: bool = False,
+                  identity_input: Optional[torch.Tensor] = None) -> None:
     """y[r] (+)= sum_k wts[r, k] Wd_e act[r, k] (+ sigmoid(shared_gate[r]) shared[r]);
-    down [E, width, ff]; y, shared float32 [rows, width]; shared_gate float32 [rows] (strided)."""
-    _cuda(act, down, ids, wts, y, shared, shared_gate)
+    down [E, width, ff]; y, shared float32 [rows, width]; shared_gate float32 [rows] (strided).
+    ``identity_input`` ([rows, width], act's type): an expert index of E or more is an identity
+    expert, whose output is that row."""
+    _cuda(act, down, ids, wts, y, shared, shared_gate, identity_input)
+    if identity_input is not None:
+        assert identity_input.dtype == act.dtype and identity_input.is_contiguous()
     rows, top, ff = act.shape
     width = down.shape[1]
     assert act.is_contiguous() and down.is_contiguous() and act.dtype == down.dtype
@@ -1223,7 +1367,9 @@ def moe_down_rows(act: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, wts:
                                    _ptr(shared_gate),
                                    shared_gate.stride(0) if shared_gate is not None else 0,
                                    _ptr(y), _dt(act), rows, width, ff, top, int(accumulate),
-                                   int(clear_shared), _stream()), "moe_down_rows")
+                                   int(clear_shared),
+                                   down.shape[0] if identity_input is not None else (1 << 30),
+                                   _ptr(identity_input), _stream()), "moe_down_rows")
 
 
 def moe_grouped_ok(h_dtype: torch.dtype, width: int, ff: int) -> bool:
@@ -1253,20 +1399,27 @@ def moe_align(ids: torch.Tensor, experts: int, bn: int, pos: torch.Tensor,
                                _ptr(tile_group), _stream()), "moe_align")
 
 
-def moe_gather(h: torch.Tensor, pos: torch.Tensor, xp: torch.Tensor, top: int) -> None:
-    """xp[pos[i]] = h[i // top]."""
-    _cuda(h, pos, xp)
+def moe_gather(h: torch.Tensor, pos: torch.Tensor, xp: torch.Tensor, top: int,
+               ids: Optional[torch.Tensor] = None, experts: int = 0) -> None:
+    """xp[pos[i]] = h[i // top] (with ``ids``: only for pairs whose expert is below ``experts``)."""
+    _cuda(h, pos, xp, ids)
     assert h.is_contiguous() and xp.is_contiguous() and h.dtype == xp.dtype
     assert h.shape[1] == xp.shape[1] and pos.numel() == h.shape[0] * top
     _check(lib().llm_moe_gather(_ptr(h), _ptr(pos), _ptr(xp), _dt(h), pos.numel(), h.shape[1], top,
-                                _stream()), "moe_gather")
+                                _ptr(ids), int(experts), _stream()), "moe_gather")
 
 
 def moe_combine(d: torch.Tensor, pos: torch.Tensor, wts: torch.Tensor, y: torch.Tensor,
                 accumulate: bool, shared: Optional[torch.Tensor] = None,
-                shared_gate: Optional[torch.Tensor] = None, clear_shared: bool = False) -> None:
-    """y[r] (+)= sum_k wts[r, k] d[pos[r, k]] (+ sigmoid(shared_gate[r]) shared[r])."""
-    _cuda(d, pos, wts, y, shared, shared_gate)
+                shared_gate: Optional[torch.Tensor] = None, clear_shared: bool = False,
+                ids: Optional[torch.Tensor] = None, experts: int = 0,
+                identity_input: Optional[torch.Tensor] = None) -> None:
+    """y[r] (+)= sum_k wts[r, k] d[pos[r, k]] (+ sigmoid(shared_gate[r]) shared[r]).  With
+    ``ids``: a pair whose expert is ``experts`` or more is an identity expert, whose output is
+    the row of ``identity_input`` ([rows, width])."""
+    _cuda(d, pos, wts, y, shared, shared_gate, ids, identity_input)
+    if ids is not None:
+        assert identity_input is not None and identity_input.stride(1) == 1
     rows, top = wts.shape
     width = y.shape[1]
     assert d.dtype == y.dtype == wts.dtype == torch.float32 and d.is_contiguous()
@@ -1275,7 +1428,11 @@ def moe_combine(d: torch.Tensor, pos: torch.Tensor, wts: torch.Tensor, y: torch.
         assert shared.dtype == torch.float32 and shared.is_contiguous()
     _check(lib().llm_moe_combine(_ptr(d), _ptr(pos), _ptr(wts), _ptr(shared), _ptr(shared_gate),
                                  shared_gate.stride(0) if shared_gate is not None else 0, _ptr(y),
-                                 rows, width, top, int(accumulate), int(clear_shared), _stream()),
+                                 rows, width, top, int(accumulate), int(clear_shared), _ptr(ids),
+                                 int(experts), _ptr(identity_input),
+                                 _dt(identity_input) if identity_input is not None else 0,
+                                 identity_input.stride(0) if identity_input is not None else 0,
+                                 _stream()),
            "moe_combine")
 
 

@@ -1,6 +1,7 @@
 from .base import (BoundCall, Segment, StepContext, Workspace, build_part, graph_safe, part_class,
                    register_part, streamed_weights_of, tensor_of, unregister_part)
-from . import norm, position, attention, latent_attention, recurrent, feed_forward, block, io  # noqa: F401  (register kinds)
+from . import (norm, position, attention, latent_attention, recurrent, pooled_attention,
+               feed_forward, block, io)  # noqa: F401  (register kinds)
 from .linear import Linear
 
 __all__ = ["BoundCall", "Segment", "StepContext", "Workspace", "build_part", "graph_safe",

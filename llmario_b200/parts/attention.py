@@ -14,6 +14,19 @@ Options that are data of the part's spec (each absent by default):
   (with its bias), before the per-head norm and the rotation;
 * tensor role ``gate`` ([heads, hidden]): head h's output is multiplied by the sigmoid of the
   h-th gate, a projection of the mixer's own input, before the output projection.
+* ``keep_first`` (with ``window``): the first so many keys of a sequence are seen from every later
+  position, at their true positions;
+* tensor role ``sink`` ([heads]): ``exp(sink_h)`` joins the denominator of head h's softmax; it has
+  no key and no value;
+* ``value_dim``: the size of a value head when it is not ``head_dim`` (the cache's row is the
+  larger of the two, the rest of a shorter row is zeros);
+* ``shared_kv``: the layer has no key and value projections (nor their norm): every call of it
+  reads the cache of an earlier call, with its own queries and mask.  The layer whose cache is
+  read says with ``cache_window`` / ``cache_keep_first`` what its readers need it to keep.
+
+The last four run through the store kernel of ``csrc/qkv_store.cu`` (which also turns adjacent
+pairs itself) and the attention call with the matching arguments; a layer without them runs as
+before.
 """
 from __future__ import annotations
 
@@ -44,6 +57,25 @@ class Attention:
         if spec.get("values", "projected") not in ("projected", "keys"):
             raise ConfigError(f"attention: values '{spec.get('values')}' (projected or keys)")
         self.values_are_keys = spec.get("values") == "keys"
+        self.keep_first = int(spec.get("keep_first") or 0)
+        self.value_dim = int(spec.get("value_dim") or self.head_dim)
+        self.shared_kv = bool(spec.get("shared_kv"))
+        self.cache_window = spec.get("cache_window", self.window)
+        self.cache_keep_first = int(spec.get("cache_keep_first", self.keep_first) or 0)
+        sink = optional_tensor_of(spec, "sink", weights)
+        self.sink = None if sink is None else \
+            sink.to(device=device, dtype=torch.float32).contiguous()
+        if self.sink is not None and self.sink.numel() != self.num_heads:
+            raise ConfigError(f"attention: a sink of {self.sink.numel()} numbers for "
+                              f"{self.num_heads} heads")
+        if self.keep_first and not self.window:
+            raise ConfigError("attention: keep_first needs a window")
+        # what the store kernel of several forms serves (see the module's text)
+        self.general = bool(self.keep_first or self.sink is not None or self.shared_kv
+                            or self.value_dim != self.head_dim)
+        if self.general:
+            self._init_general(spec, weights, dtype, device)
+            return
         refusal = kernels.attention_refusal(self.num_heads, self.num_kv_heads, self.head_dim)
         if refusal is not None:      # now, when the model is built, not at its first step
             raise ConfigError(f"attention: {refusal}")
@@ -104,17 +136,92 @@ class Attention:
                              None if self.qkv_proj.bias is None else self.qkv_proj.bias[:self.q_width])
         self.o_proj = Linear(tensor_of(spec, "o", weights), b["o"])
 
+    def _init_general(self, spec: PartSpec, weights, dtype, device) -> None:
+        if self.chunk is not None or self.values_are_keys or spec["tensors"].get("gate"):
+            raise ConfigError("attention: kept first keys, a sink, shared keys and values or a "
+                              "value size of its own do not combine with a chunked mask, "
+                              "values that are keys or a gate per head")
+        d, dv = self.head_dim, self.value_dim
+        self.cache_dim = max(d, dv)
+        refusal = kernels.attention_refusal(self.num_heads, self.num_kv_heads, self.cache_dim)
+        if refusal is not None:
+            raise ConfigError(f"attention: {refusal}")
+        self.position = (build_part("position", spec["position"], weights, dtype, device)
+                         if spec.get("position") is not None else None)
+        if self.position is not None and not hasattr(self.position, "head_permutation"):
+            raise ConfigError("attention: with these options the rotation is that of adjacent "
+                              "pairs (rope_normal)")
+        qn, kn = spec.get("q_norm"), spec.get("k_norm")
+        self.q_norm = build_part("norm", qn, weights, dtype, device) if qn is not None else None
+        self.k_norm = build_part("norm", kn, weights, dtype, device) if kn is not None else None
+        if self.q_norm is not None and self.k_norm is not None and \
+                self.q_norm.eps != self.k_norm.eps:
+            raise ValueError("q_norm and k_norm must share eps")
+        if (self.q_norm is None) != (self.k_norm is None) and not self.shared_kv:
+            raise ValueError("q_norm and k_norm come together")
+        self.q_width = self.num_heads * d
+        self.k_cols, self.v_cols = self.num_kv_heads * d, self.num_kv_heads * dv
+        mats = [tensor_of(spec, "q", weights)]
+        if not self.shared_kv:
+            mats += [tensor_of(spec, "k", weights), tensor_of(spec, "v", weights)]
+        n_rows = sum(m.shape[0] for m in mats)
+        if n_rows % 16:
+            mats.append(torch.zeros(16 - n_rows % 16, self.hidden, dtype=mats[0].dtype,
+                                    device=mats[0].device))
+        self.qkv_proj = Linear.stacked(mats)
+        # (attention writes value_dim channels per head, so the projection is as stored)
+        self.o_proj = Linear(tensor_of(spec, "o", weights))
+
     def cache_need(self):
         # (no query ever looks back further than a chunk is long: pages behind that go back)
+        if self.general:
+            return PagedKV(self.num_kv_heads, self.cache_dim, self.cache_window,
+                           self.cache_keep_first if self.cache_window else 0)
         return PagedKV(self.num_kv_heads, self.head_dim, self.window or self.chunk)
 
     def streamed_weights(self):
         """The matrices a step reads once: q, k, v (stacked) and the output projection."""
         return [self.qkv_proj.weight, self.o_proj.weight]
 
+    def _forward_general(self, ctx: StepContext, call: BoundCall, h: torch.Tensor,
+                         x: torch.Tensor, accumulate: bool) -> None:
+        rows, d, dv, hd = ctx.rows, self.head_dim, self.value_dim, self.cache_dim
+        view = ctx.cache.view(call.cache_entry)
+        if view is None:
+            raise RuntimeError(f"run-order entry {call.index}: attention needs a cache")
+        if self.shared_kv and call.writes_cache:
+            raise RuntimeError(f"run-order entry {call.index}: a layer without key and value "
+                               "projections must read another call's cache")
+        writes = call.writes_cache
+        proj = ctx.buffer("attn.gproj", (rows, self.qkv_proj.out_features), torch.float32)
+        self.qkv_proj(h, proj)
+        cos_sin, rot = None, 0
+        if self.position is not None:
+            _, rot, _ = self.position.rotary_tables()
+            cos_sin = self.position.step_angles(ctx)
+        q = ctx.buffer("attn.q", (rows, self.num_heads * hd))
+        norm = kernels.NORM_PER_HEAD if self.q_norm is not None else kernels.NORM_NONE
+        kernels.qkv_store(
+            proj[:, :self.q_width],
+            proj[:, self.q_width:self.q_width + self.k_cols] if writes else None,
+            proj[:, self.q_width + self.k_cols:self.q_width + self.k_cols + self.v_cols]
+            if writes else None,
+            q, view, ctx.row_slot, ctx.row_pos, self.num_heads, self.num_kv_heads, d, dv, hd,
+            norm, self.q_norm.weight if self.q_norm is not None else None,
+            self.k_norm.weight if self.k_norm is not None and writes else None,
+            self.q_norm.eps if self.q_norm is not None else 0.0, rot, cos_sin)
+        out = ctx.buffer("attn.out", (rows, self.num_heads * dv))
+        driver.attention(ctx, q, out, view, self.num_heads, self.num_kv_heads, hd, self.scale,
+                         self.mask, sink=self.sink, value_dim=dv if dv != hd else None,
+                         keep_first=self.keep_first)
+        self.o_proj(out, x, accumulate=accumulate)
+
     def forward(self, ctx: StepContext, call: BoundCall, h: torch.Tensor, x: torch.Tensor,
                 accumulate: bool = True) -> None:
         """Adds the result into ``x``; with ``accumulate=False`` ``x`` (float32) receives it."""
+        if self.general:
+            self._forward_general(ctx, call, h, x, accumulate)
+            return
         rows = ctx.rows
         view = ctx.cache.view(call.cache_entry)
         if view is None:

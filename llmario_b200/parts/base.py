@@ -164,6 +164,14 @@ class BoundCall:
                          self.cache_entries)
 
 
+def cache_needs_of(mixer) -> List[Any]:
+    """What a mixer keeps between steps, one need per thing: its own list (``cache_needs()``,
+    for a mixer with several: two caches, a cache and a state) or its single ``cache_need()``.
+    Such a mixer finds the k-th need's cache entry with ``call.for_need(k)``."""
+    fn = getattr(mixer, "cache_needs", None)
+    return list(fn()) if fn is not None else [mixer.cache_need()]
+
+
 def streamed_weights_of(part) -> List[torch.Tensor]:
     """The matrices a part reads once per step, as the part itself declares them
     (``streamed_weights()``).  A part that declares nothing cannot be counted."""

@@ -9,8 +9,8 @@ import torch
 
 from .. import kernels
 from ..config.spec import ConfigError, LayerSpec, PartSpec
-from .base import (BoundCall, StepContext, build_part, graph_safe, optional_tensor_of,
-                   register_part, streamed_weights_of)
+from .base import (BoundCall, StepContext, build_part, cache_needs_of, graph_safe,
+                   optional_tensor_of, register_part, streamed_weights_of)
 from .norm import RmsNorm
 
 
@@ -31,7 +31,7 @@ class PreNormResidualBlock:
         """What this block keeps between steps: one need per stateful part, in a fixed order
         (here the mixer's alone).  Each need gets a cache entry; ``call.for_need(k)`` is the
         call as the owner of the k-th need sees it."""
-        return [self.mixer.cache_need()]
+        return cache_needs_of(self.mixer)
 
     def streamed_weights(self):
         return streamed_weights_of(self.mixer) + streamed_weights_of(self.feed_forward)
@@ -55,7 +55,10 @@ class OutputNormResidualBlock:
     ``x += s1 * norm1(mixer(x)); x += s2 * norm2(feed_forward(x))``.  The sublayers read the
     residual stream itself (rounded to the activation type); norm, scale and sum are 32-bit and
     one kernel.  A layer whose feed-forward is of kind ``none`` has only the first sublayer; the
-    scales (tensor roles ``mixer_scale`` / ``feed_forward_scale``) are optional."""
+    scales (tensor roles ``mixer_scale`` / ``feed_forward_scale``) are optional.
+
+    With ``mixer_input_norm`` / ``feed_forward_input_norm`` a sublayer has a norm on both sides:
+    ``x += norm_out(sublayer(norm_in(x)))``."""
 
     def __init__(self, spec: PartSpec, layer: LayerSpec, weights: Dict[str, torch.Tensor],
                  dtype, device):
@@ -63,7 +66,13 @@ class OutputNormResidualBlock:
             t = optional_tensor_of(spec, role, weights) if spec.get("tensors") else None
             return None if t is None else t.to(device=device, dtype=torch.float32).contiguous()
 
+        def input_norm(key):
+            return None if spec.get(key) is None else build_part("norm", spec[key], weights,
+                                                                   dtype, device)
+
         self.mixer_norm = build_part("norm", spec["mixer_norm"], weights, dtype, device)
+        self.mixer_in = input_norm("mixer_input_norm")
+        self.ffn_in = input_norm("feed_forward_input_norm")
         self.mixer_scale = scale("mixer_scale")
         self.mixer = build_part("mixer", layer.mixer, weights, dtype, device)
         self.feed_forward = build_part("feed_forward", layer.feed_forward, weights, dtype,
@@ -74,12 +83,12 @@ class OutputNormResidualBlock:
             self.ffn_norm = build_part("norm", spec["feed_forward_norm"], weights, dtype, device)
             self.ffn_scale = scale("feed_forward_scale")
         for norm in (self.mixer_norm, self.ffn_norm):
-            if norm is not None and type(norm) is not RmsNorm:
+            if norm is not None and not isinstance(norm, RmsNorm):
                 raise ConfigError("the output-norm block fuses an RMS norm with the residual "
                                   f"sum; it has no form for {type(norm).__name__}")
 
     def cache_needs(self):
-        return [self.mixer.cache_need()]
+        return cache_needs_of(self.mixer)
 
     def streamed_weights(self):
         return streamed_weights_of(self.mixer) + streamed_weights_of(self.feed_forward)
@@ -89,11 +98,16 @@ class OutputNormResidualBlock:
         return graph_safe(self.mixer) and graph_safe(self.feed_forward)
 
     @staticmethod
-    def _input(ctx: StepContext, x: torch.Tensor, have: bool) -> torch.Tensor:
-        """The residual stream as a sublayer reads it: rounded to the activation type.
+    def _input(ctx: StepContext, x: torch.Tensor, have: bool, norm=None) -> torch.Tensor:
+        """The residual stream as a sublayer reads it: rounded to the activation type, or
+        through the sublayer's input norm when it has one.
         ``have``: the kernel that last added into the stream has left the rounded copy behind
         (see ``_add``); else (the first sublayer behind the embedding, or behind a block of
         another kind) it is rounded here."""
+        if norm is not None:
+            h = ctx.buffer("block.h", x.shape)
+            norm.apply(ctx, x, h)
+            return h
         if ctx.dtype == torch.float32:
             return x                   # the sublayer only reads it; x changes after it is done
         h = ctx.buffer("block.h", x.shape)
@@ -102,9 +116,9 @@ class OutputNormResidualBlock:
         return h
 
     @staticmethod
-    def _add(ctx: StepContext, y, norm, scale, x, clear: bool) -> None:
-        """x += scale * norm(y), and the next sublayer's input beside it."""
-        h = ctx.buffer("block.h", x.shape) if ctx.dtype != torch.float32 else None
+    def _add(ctx: StepContext, y, norm, scale, x, clear: bool, rounded: bool = True) -> None:
+        """x += scale * norm(y), and (``rounded``) the next sublayer's input beside it."""
+        h = ctx.buffer("block.h", x.shape) if ctx.dtype != torch.float32 and rounded else None
         kernels.norm_scale_add(y, norm.weight, scale, x, norm.eps, rounded=h, clear=clear)
 
     def forward(self, ctx: StepContext, call: BoundCall, x: torch.Tensor) -> None:
@@ -117,10 +131,14 @@ class OutputNormResidualBlock:
         # the run-order entry just before this one was a block of this kind on the same stream
         have = ctx.shared.get("block.h behind") == (x.data_ptr(), call.index - 1)
         self.mixer.forward(ctx, call.for_need(0) if call.cache_entries else call,
-                           self._input(ctx, x, have), y, accumulate=kept_zero)
-        self._add(ctx, y, self.mixer_norm, self.mixer_scale, x, kept_zero)
+                           self._input(ctx, x, have, self.mixer_in), y, accumulate=kept_zero)
+        # (the rounded stream is left behind only for a sublayer that reads it as it is)
+        last = not self.has_feed_forward
+        self._add(ctx, y, self.mixer_norm, self.mixer_scale, x, kept_zero,
+                  rounded=self.ffn_in is None if not last else True)
         if self.has_feed_forward:
-            self.feed_forward.forward(ctx, self._input(ctx, x, True), y, accumulate=kept_zero)
+            self.feed_forward.forward(ctx, self._input(ctx, x, True, self.ffn_in), y,
+                                      accumulate=kept_zero)
             self._add(ctx, y, self.ffn_norm, self.ffn_scale, x, kept_zero)
         ctx.shared["block.h behind"] = (x.data_ptr(), call.index)
 
@@ -164,7 +182,7 @@ class HyperConnectionBlock:
                                   f"of the streams; it has no form for {type(norm).__name__}")
 
     def cache_needs(self):
-        return [self.mixer.cache_need()]
+        return cache_needs_of(self.mixer)
 
     def streamed_weights(self):
         return streamed_weights_of(self.mixer) + streamed_weights_of(self.feed_forward)

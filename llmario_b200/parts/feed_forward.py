@@ -6,7 +6,13 @@ Beside it: the same form with a choice of activation and optional biases (kind `
 routed experts (kind ``moe``): a router's logits (32-bit) choose ``top`` of ``experts`` small
 silu-gated feed-forwards per token, whose outputs are summed with the softmax over the chosen
 logits as weights; an optional shared feed-forward is applied to all tokens and added with a
-per-token scalar weight, the sigmoid of one more projection of the input."""
+per-token scalar weight, the sigmoid of one more projection of the input.  Options of the routed
+experts: ``scores: "softmax_all"`` (the scores are the softmax over all router outputs, the choice
+goes by score plus the tensor ``correction``, and a chosen expert's weight is its score, not
+renormalised); ``identity`` (the last so many router outputs are experts without matrices whose
+output is the input itself); ``activation: "clamped_swish"`` with ``limit``.
+
+And a feed-forward without a gate (kind ``dense``): ``y = W_down act(W_up h)``."""
 from __future__ import annotations
 
 from typing import Dict
@@ -118,6 +124,36 @@ class GatedFeedForward:
         self.down(act, x, accumulate=accumulate)
 
 
+class DenseFeedForward:
+    """``y = W_down act(W_up h)`` with ``activation`` ``relu_squared`` (max(z, 0)^2)."""
+
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
+        self.hidden = int(spec["hidden_size"])
+        self.ff = int(spec["intermediate_size"])
+        self.activation = spec.get("activation", "relu_squared")
+        if self.activation not in kernels.PLAIN_ACTIVATIONS:
+            raise ConfigError(f"dense feed-forward: activation '{self.activation}' (known: "
+                              f"{', '.join(kernels.PLAIN_ACTIVATIONS)})")
+        self.up = Linear(tensor_of(spec, "up", weights))
+        self.down = Linear(tensor_of(spec, "down", weights))
+
+    def streamed_weights(self):
+        return [self.up.weight, self.down.weight]
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, x: torch.Tensor,
+                accumulate: bool = True) -> None:
+        rows = ctx.rows
+        kept_zero = rows <= kernels.SPLIT_K_MAX_ROWS
+        u = ctx.buffer("ffn.up.z" if kept_zero else "ffn.up", (rows, self.ff), torch.float32,
+                       zero=kept_zero)
+        self.up(h, u, out_is_zero=kept_zero)
+        act = ctx.buffer("ffn.act", (rows, self.ff))
+        kernels.act_rows(u, act, self.activation, clear=kept_zero)
+        self.down(act, x, accumulate=accumulate)
+
+
 class RoutedExperts:
     graph_safe = True      # which experts a row uses is read on the device
     grouped = True         # (False: always the row-wise kernels; for comparisons)
@@ -127,11 +163,30 @@ class RoutedExperts:
         self.ff = ff = int(spec["intermediate_size"])
         self.experts = E = int(spec["experts"])
         self.top = int(spec["top"])
-        if not 1 <= self.top <= min(E, 16):
-            raise ConfigError(f"routed experts: top {self.top} of {E} (at most 16)")
+        self.identity = int(spec.get("identity") or 0)       # experts without matrices
+        self.routed = E + self.identity                      # router outputs that can be chosen
+        self.scores = spec.get("scores", "softmax_chosen")
+        self.activation = spec.get("activation", "silu")
+        self.limit = float(spec.get("limit") or 0.0)
+        if self.scores not in ("softmax_chosen", "softmax_all"):
+            raise ConfigError(f"routed experts: scores '{self.scores}'")
+        if self.activation not in ("silu", "clamped_swish"):
+            raise ConfigError(f"routed experts: activation '{self.activation}'")
+        if not 1 <= self.top <= min(self.routed, 16):
+            raise ConfigError(f"routed experts: top {self.top} of {self.routed} (at most 16)")
         router = tensor_of(spec, "router", weights).to(torch.float32)
+        if router.shape[0] != self.routed:
+            raise ConfigError(f"routed experts: a router of {router.shape[0]} outputs for "
+                              f"{E} experts and {self.identity} identity experts")
+        corr = optional_tensor_of(spec, "correction", weights)
+        self.correction = None if corr is None else \
+            corr.to(device=router.device, dtype=torch.float32).contiguous()
+        if self.correction is not None and self.scores != "softmax_all":
+            raise ConfigError("routed experts: a correction of the choice needs scores "
+                              "'softmax_all'")
         bias = optional_tensor_of(spec, "router_bias", weights)
-        bias = torch.zeros(E, device=router.device) if bias is None else bias.to(torch.float32)
+        bias = torch.zeros(self.routed, device=router.device) if bias is None \
+            else bias.to(torch.float32)
         sg = optional_tensor_of(spec, "shared_gate", weights)
         self.shared = None
         if spec.get("shared") is not None:
@@ -158,14 +213,17 @@ class RoutedExperts:
     def forward(self, ctx: StepContext, h: torch.Tensor, x: torch.Tensor,
                 accumulate: bool = True) -> None:
         rows, E, top = ctx.rows, self.experts, self.top
+        R = self.routed
         z = ctx.buffer("moe.logits", (rows, self.router.out_features), torch.float32)
         ids = ctx.buffer("moe.ids", (rows, top), torch.int32)
         wts = ctx.buffer("moe.weights", (rows, top), torch.float32)
         if (self.hidden + self.router.out_features) * 4 <= 200 * 1024:
-            kernels.moe_router(h, self.router.weight, self.router.bias, E, top, z, ids, wts)
+            kernels.moe_router(h, self.router.weight, self.router.bias, R, top, z, ids, wts,
+                               self.scores, self.correction)
         else:           # a row too wide to stage: the product, then the choice
             self.router(h, z)
-            kernels.moe_route(z, E, top, ids, wts)
+            kernels.moe_route(z, R, top, ids, wts, self.scores, self.correction)
+        ident = h if self.identity else None
         shared = gate = None
         kept_zero = rows <= kernels.SPLIT_K_MAX_ROWS
         if self.shared is not None:
@@ -174,7 +232,7 @@ class RoutedExperts:
             shared = ctx.buffer("moe.shared.z" if kept_zero else "moe.shared", (rows, self.hidden),
                                 torch.float32, zero=kept_zero)
             self.shared.forward(ctx, h, shared, accumulate=kept_zero)
-            gate = z[:, E]
+            gate = z[:, R]
         if kernels.moe_grouped_ok(h.dtype, self.hidden, self.ff) and self.grouped:
             # sorted by expert into tiles of rows, two grouped tensor-core products, one sum
             pairs = rows * top
@@ -184,20 +242,28 @@ class RoutedExperts:
             tile_group = ctx.buffer("moe.tiles", (tiles,), torch.int32)
             kernels.moe_align(ids, E, bn, pos, tile_group)
             xp = ctx.buffer("moe.x", (tiles * bn, self.hidden))
-            kernels.moe_gather(h, pos, xp, top)
+            kernels.moe_gather(h, pos, xp, top, ids if self.identity else None, E)
             act = ctx.buffer("moe.act", (tiles * bn, self.ff))
-            kernels.gemm_grouped(xp, self.gate_up, act, tile_group, bn, gated=True)
+            if self.activation == "silu":
+                kernels.gemm_grouped(xp, self.gate_up, act, tile_group, bn, gated=True)
+            else:       # the product as it is, then the activation over the padded buffer
+                gu = ctx.buffer("moe.gate_up", (tiles * bn, 2 * self.ff), torch.float32)
+                kernels.gemm_grouped(xp, self.gate_up, gu, tile_group, bn, gated=False)
+                kernels.gated_act(gu, None, act, self.activation, limit=self.limit)
             d = ctx.buffer("moe.down", (tiles * bn, self.hidden), torch.float32)
             kernels.gemm_grouped(act, self.down, d, tile_group, bn, gated=False)
-            kernels.moe_combine(d, pos, wts, x, accumulate, shared, gate, clear_shared=kept_zero)
+            kernels.moe_combine(d, pos, wts, x, accumulate, shared, gate, clear_shared=kept_zero,
+                                ids=ids if self.identity else None, experts=E,
+                                identity_input=ident)
             return
         act = ctx.buffer("moe.act", (rows, top, self.ff))
-        kernels.moe_gate_up_rows(h, self.gate_up, ids, act)
+        kernels.moe_gate_up_rows(h, self.gate_up, ids, act, self.activation, self.limit)
         kernels.moe_down_rows(act, self.down, ids, wts, x, accumulate, shared, gate,
-                              clear_shared=kept_zero)
+                              clear_shared=kept_zero, identity_input=ident)
 
 
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)
 register_part("feed_forward", "gated", GatedFeedForward, replace=True)
 register_part("feed_forward", "moe", RoutedExperts, replace=True)
+register_part("feed_forward", "dense", DenseFeedForward, replace=True)
 register_part("feed_forward", "none", NoFeedForward, replace=True)

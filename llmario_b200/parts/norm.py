@@ -25,4 +25,18 @@ class RmsNorm:
         kernels.rms_norm(x, self.weight, out, self.eps, rows_index)
 
 
+class ScalarRmsNorm(RmsNorm):
+    """RMS norm whose gain is one stored number for all coordinates (a tensor without
+    dimensions).  It is spread over the width once, so every kernel that takes a gain per
+    channel takes this norm as well."""
+
+    def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
+        self.width = int(spec["width"])
+        self.eps = float(spec["eps"])
+        gain = tensor_of(spec, "weight", weights).to(device=device, dtype=torch.float32)
+        assert gain.numel() == 1
+        self.weight = gain.reshape(1).expand(self.width).contiguous()
+
+
 register_part("norm", "rms_norm", RmsNorm, replace=True)
+register_part("norm", "rms_norm_scalar", ScalarRmsNorm, replace=True)

@@ -19,7 +19,12 @@
   ``f = log sigmoid(cap tanh((W_f h + b_f) / cap))``; each head's output is divided by its root
   mean square, multiplied by a gain per channel and by ``sigmoid(W_g h)``, and projected.
 
-All are the same recurrence (``csrc/recurrent.cu``), told by data how the decay is made (the
+* ``min_gru``: a vector state per channel whose gates read only the current token:
+  ``S_t = (1 - z_t) S_(t-1) + z_t c_t`` with ``z = sigmoid(W_z h + b_z)`` and the candidate
+  ``c = u + 1/2`` where ``u = W_x h + b_x >= 0`` and ``sigmoid(u)`` elsewhere; the output is
+  ``W_o (S_t silu(W_g h))``.  It has a kernel of its own (a multiply-add per token and channel).
+
+The first three are the same recurrence (``csrc/recurrent.cu``), told by data how the decay is made (the
 matrix memory's normaliser is one more state column that is fed ones).  The
 state (and the convolution's last inputs) is 32-bit and lives in the request's fixed-size state
 slot of the cache manager, which clears a slot when a request is opened in it.  Everything
@@ -263,6 +268,59 @@ class MatrixMemory:
         self.o_proj(gated, x, accumulate=accumulate)
 
 
+class MinGru:
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
+        self.hidden = int(spec["hidden_size"])
+        self.width = int(spec["width"])
+        t = {r: tensor_of(spec, r, weights) for r in ("z", "x", "g", "o")}
+        for r in ("z", "x", "g"):
+            if tuple(t[r].shape) != (self.width, self.hidden):
+                raise ConfigError(f"min_gru: tensor '{r}' of {list(t[r].shape)} for a state of "
+                                  f"{self.width} channels on a width of {self.hidden}")
+        # the three projections of the mixer's input are one product; each keeps a column range
+        # of whole 16-byte units
+        self.stride = -(-self.width // 4) * 4
+        pad = self.stride - self.width
+
+        def padded(m):
+            return m if not pad else torch.cat(
+                [m, torch.zeros(pad, self.hidden, dtype=m.dtype, device=m.device)])
+
+        self.in_proj = _padded_rows([padded(t["z"]), padded(t["x"]), padded(t["g"])], self.hidden)
+        bz, bx = (optional_tensor_of(spec, r, weights) for r in ("z_bias", "x_bias"))
+        self.bias_z = None if bz is None else _f32(bz, device)
+        self.bias_x = None if bx is None else _f32(bx, device)
+        self.o_proj = Linear(t["o"])
+
+    def cache_need(self):
+        return FixedState((self.width,), torch.float32)
+
+    def streamed_weights(self):
+        return [self.in_proj.weight, self.o_proj.weight]
+
+    def run(self, ctx: StepContext, call: BoundCall, proj: torch.Tensor, x: torch.Tensor,
+            accumulate: bool) -> None:
+        """From the projections ``proj`` = [z | x | g] (float32, column ranges of ``stride``
+        channels each, overwritten) to the output, added into or written to ``x``."""
+        state = ctx.cache.state_of(call.cache_entry)
+        if state is None:
+            raise RuntimeError(f"run-order entry {call.index}: the recurrence needs a state slot")
+        n, W = self.stride, self.width
+        gated = ctx.buffer("mingru.gated", (ctx.rows, W))
+        kernels.min_gru(proj[:, :W], proj[:, n:n + W], proj[:, 2 * n:2 * n + W], self.bias_z,
+                        self.bias_x, state, gated, ctx.row_slot, step_segments(ctx))
+        self.o_proj(gated, x, accumulate=accumulate)
+
+    def forward(self, ctx: StepContext, call: BoundCall, h: torch.Tensor, x: torch.Tensor,
+                accumulate: bool = True) -> None:
+        proj = ctx.buffer("mingru.proj", (ctx.rows, self.in_proj.out_features), torch.float32)
+        self.in_proj(h, proj)
+        self.run(ctx, call, proj, x, accumulate)
+
+
+register_part("mixer", "min_gru", MinGru, replace=True)
 register_part("mixer", "gla", GatedLinearAttention, replace=True)
 register_part("mixer", "mlstm", MatrixMemory, replace=True)
 register_part("mixer", "mamba2", StateSpaceMixer, replace=True)

@@ -126,7 +126,7 @@ def load_weights(model_dir: str, spec: ModelSpec, dtype: torch.dtype,
 def random_tensors(spec: ModelSpec, seed: int, dtype: torch.dtype,
                    device: torch.device | str = "cpu", matrix_std: float = 0.02,
                    gain_std: float = 0.01) -> Dict[str, torch.Tensor]:
-    """Seeded weights: matrices ~ N(0, matrix_std), one-dimensional gains 1 + N(0, gain_std).
+    """Seeded weights: matrices ~ N(0, matrix_std), one-dimensional gains (and single numbers) 1 + N(0, gain_std).
     Every element is a function of (seed, tensor name, element index) alone
     (:mod:`.random_normal`): the values are the same bits on a CUDA device (made by the kernel
     of ``csrc/random_weights.cu``) and on the host (made by NumPy), and do not depend on the
@@ -138,7 +138,7 @@ def random_tensors(spec: ModelSpec, seed: int, dtype: torch.dtype,
     for name, shape in expected_tensors(spec).items():
         key = tensor_key(seed, name)
         shape = tuple(FREE_DIM_DEFAULT if d is None else d for d in shape)
-        mean, std = (1.0, gain_std) if len(shape) == 1 else (0.0, matrix_std)
+        mean, std = (1.0, gain_std) if len(shape) <= 1 else (0.0, matrix_std)
         t = torch.empty(shape, dtype=dtype, device=device)
         if device.type == "cuda":
             from .. import kernels

@@ -19,12 +19,16 @@ class PlainError(RuntimeError):
 
 
 class PlainCache:
-    """``windows[g]``: keys a query of group g sees (None = all); ``n_pages[g]``: its pool."""
+    """``windows[g]``: keys a query of group g sees (None = all); ``n_pages[g]``: its pool;
+    ``keeps[g]``: with a window, the first so many keys stay; ``everys[g]``: tokens per entry."""
 
     def __init__(self, n_pages: Sequence[int], windows: Sequence[Optional[int]], page_size: int,
-                 max_requests: int, max_context: int, has_state: bool = False):
+                 max_requests: int, max_context: int, has_state: bool = False,
+                 keeps: Optional[Sequence[int]] = None, everys: Optional[Sequence[int]] = None):
         self.page_size, self.max_requests, self.max_context = page_size, max_requests, max_context
         self.windows, self.has_state = list(windows), has_state
+        self.keeps = list(keeps) if keeps is not None else [0] * len(n_pages)
+        self.everys = list(everys) if everys is not None else [1] * len(n_pages)
         self.free: List[Deque[int]] = [deque(range(n)) for n in n_pages]
         self.n_pages = list(n_pages)
         self.requests: Dict[Any, dict] = {}
@@ -52,10 +56,16 @@ class PlainCache:
         w = self.windows[g]
         return 0 if w is None else max(0, length - w + 1) // self.page_size
 
+    def _kept_pages(self, g):
+        return 0 if self.windows[g] is None else -(-self.keeps[g] // self.page_size)
+
+    def _pages_for(self, g, length):
+        return -(-(length // self.everys[g]) // self.page_size)
+
     def pages_needed(self, rid, n):
         r = self._req(rid)
-        want = -(-(r["length"] + n) // self.page_size)
-        return [max(0, want - len(p)) for p in r["pages"]]
+        return [max(0, self._pages_for(g, r["length"] + n) - len(p))
+                for g, p in enumerate(r["pages"])]
 
     def reserve(self, growth):
         need = [0] * len(self.n_pages)
@@ -84,12 +94,12 @@ class PlainCache:
 
     def advance(self, rid, n):
         r = self._req(rid)
-        if any(r["length"] + n > len(p) * self.page_size for p in r["pages"]):
+        if any(self._pages_for(g, r["length"] + n) > len(p) for g, p in enumerate(r["pages"])):
             raise PlainError("advanced past reserved pages")
         r["length"] += n
         for g in range(len(self.n_pages)):
             keep_from = min(self._first_needed(g, r["length"]), len(r["pages"][g]))
-            for j in range(r["first_live"][g], keep_from):
+            for j in range(max(r["first_live"][g], self._kept_pages(g)), keep_from):
                 self.free[g].append(r["pages"][g][j])
                 r["pages"][g][j] = -1
                 self.updates[g][(r["slot"], j)] = -1
@@ -102,10 +112,10 @@ class PlainCache:
         if self.has_state and length < r["length"]:
             raise PlainError("state")
         for g in range(len(self.n_pages)):
-            if self._first_needed(g, length) < r["first_live"][g]:
+            if max(self._first_needed(g, length), self._kept_pages(g)) < r["first_live"][g]:
                 raise PlainError("window gone")
-        keep = -(-length // self.page_size)
         for g in range(len(self.n_pages)):
+            keep = self._pages_for(g, length)
             for j in range(keep, len(r["pages"][g])):
                 if r["pages"][g][j] >= 0:
                     self.free[g].append(r["pages"][g][j])
