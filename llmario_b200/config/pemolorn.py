@@ -197,14 +197,14 @@ class PemolornConfig:
             if layer.type == "parallel":
                 left, right = m["left"], m["right"]
                 H, G, d, dv = left["heads"], left["kv_heads"], left["dim"], left["vdim"]
-                taps = int(left.get("conv") or 1)
+                taps = int(left.get("conv") or 0)
                 rot = left.get("rot")
                 lx = x + "left."
                 t = {"q": (lx + "q", (H * d, W)), "k": (lx + "k", (G * d, W)),
                      "v": (lx + "v", (G * dv, W)), "o": (lx + "o", (W, H * dv)),
                      "q_norm": (lx + "q.norm", (H * d,)), "k_norm": (lx + "k.norm", (G * d,)),
                      "sink": (lx + "sink", (H,))}
-                if taps > 1:
+                if taps >= 1:      # (one tap: a weight per channel)
                     t.update(q_conv=(lx + "q.conv", (H * d, taps)),
                              k_conv=(lx + "k.conv", (G * d, taps)),
                              v_conv=(lx + "v.conv", (G * dv, taps)))

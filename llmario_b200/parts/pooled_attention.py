@@ -46,9 +46,9 @@ class PooledWindowAttention:
         self.scale = float(spec["scale"])
         self.window = int(spec["window"])
         self.pool = int(spec.get("pool") or 0)
-        self.taps = int(spec.get("conv_taps") or 1)
+        self.taps = int(spec.get("conv_taps") or 0)
         self.eps = float(spec["eps"])
-        if self.window < 1 or self.pool < 0 or self.taps < 1 or H % G:
+        if self.window < 1 or self.pool < 0 or self.taps < 0 or H % G:
             raise ConfigError(f"pooled attention: window {self.window}, pool {self.pool}, "
                               f"{self.taps} taps, {H} heads on {G} key heads")
         refusal = kernels.attention_refusal(H, G, self.cache_dim)
@@ -73,7 +73,7 @@ class PooledWindowAttention:
             raise ConfigError("pooled attention: the norms have a weight per channel of the "
                               "whole query and key rows")
         self.conv_weight = None
-        if self.taps > 1:
+        if self.taps >= 1:
             conv = [tensor_of(spec, r + "_conv", weights) for r in ("q", "k", "v")]
             for c, n in zip(conv, (self.q_cols, self.k_cols, self.v_cols)):
                 if tuple(c.shape) != (n, self.taps):
@@ -109,8 +109,10 @@ class PooledWindowAttention:
         view = ctx.cache.view(call.for_need(0).cache_entry)
         pooled = ctx.cache.view(call.for_need(1).cache_entry) if self.pool else None
         src = proj[:, :self.channels]
-        if self.taps > 1:
-            state = ctx.cache.state_of(call.for_need(2 if self.pool else 1).cache_entry)
+        if self.taps >= 1:
+            # (one tap keeps no inputs: a weight per channel, and the kernel reads no history)
+            state = ctx.cache.state_of(call.for_need(2 if self.pool else 1).cache_entry) \
+                if self.taps > 1 else ctx.buffer("pattn.nohist", (1, 1), torch.float32)
             conv = ctx.buffer("pattn.conv", (rows, self.channels), torch.float32)
             kernels.causal_conv_silu(src, self.conv_weight, None, state, conv, ctx.row_slot,
                                      step_segments(ctx), activation=False)

@@ -174,15 +174,23 @@ def dense_ff(h, t, p):
     return np.maximum(h @ t[p + "up"].T, 0.0) ** 2 @ t[p + "down"].T
 
 
-def route(h, t, p, mlp):
+def route(h, t, p, mlp, margins: Optional[list] = None):
     """(chosen [T, top], weights [T, top]): softmax over all router outputs, the choice by the
-    score plus a correction, the weight the score itself."""
+    score plus a correction, the weight the score itself.  ``margins`` collects, per token, how
+    far the last chosen choice score lies above the best one not chosen, in units of the larger
+    of the two softmax scores (a move of a logit by x moves its score by about x times itself)."""
     z = h @ t[p + "router"].T
     z = z - z.max(axis=-1, keepdims=True)
     s = np.exp(z) / np.exp(z).sum(axis=-1, keepdims=True)
     choice = s + t[p + "correction"]
     top = int(mlp["router"]["top"])
-    chosen = np.argsort(-choice, axis=-1, kind="stable")[:, :top]
+    order = np.argsort(-choice, axis=-1, kind="stable")
+    chosen = order[:, :top]
+    if margins is not None and top < s.shape[1]:
+        a, b = order[:, top - 1:top], order[:, top:top + 1]
+        gap = np.take_along_axis(choice, a, -1) - np.take_along_axis(choice, b, -1)
+        unit = np.maximum(np.take_along_axis(s, a, -1), np.take_along_axis(s, b, -1))
+        margins.append((gap / unit)[:, 0])
     return chosen, np.take_along_axis(s, chosen, axis=-1)
 
 
@@ -192,10 +200,10 @@ def expert(h, t, p, limit):
     return (g * sigmoid(1.702 * g) * (u + 1.0)) @ t[p + "down"].T
 
 
-def moe_ff(h, t, p, mlp):
+def moe_ff(h, t, p, mlp, margins: Optional[list] = None):
     E = int(mlp["router"]["experts"])
     limit = float(mlp["expert"]["limit"])
-    chosen, w = route(h, t, p, mlp)
+    chosen, w = route(h, t, p, mlp, margins)
     out = np.zeros_like(h)
     for i in range(h.shape[0]):
         for e, we in zip(chosen[i], w[i]):
@@ -206,8 +214,9 @@ def moe_ff(h, t, p, mlp):
 
 # --------------------------------------------------------------------------------------------
 def forward(cfg: dict, tensors: Dict[str, np.ndarray], tokens, layers_out: Optional[List] = None,
-            round_cache: Callable = lambda a: a):
-    """Logits [T, vocab] of one sequence from position 0."""
+            round_cache: Callable = lambda a: a, margins: Optional[list] = None):
+    """Logits [T, vocab] of one sequence from position 0.  ``layers_out`` collects the residual
+    stream behind every layer, ``margins`` the routers' margins per token (see :func:`route`)."""
     t = {n: np.asarray(a, F) for n, a in tensors.items()}
     eps = float(cfg["norm"]["eps"])
     x = t["embed"][np.asarray(tokens)]
@@ -227,7 +236,7 @@ def forward(cfg: dict, tensors: Dict[str, np.ndarray], tokens, layers_out: Optio
         if mlp is not None:
             h = scalar_norm(x, t[p + "norm2"], eps)
             y = dense_ff(h, t, p + "mlp.") if mlp.get("kind", "dense") == "dense" \
-                else moe_ff(h, t, p + "mlp.", mlp)
+                else moe_ff(h, t, p + "mlp.", mlp, margins)
             x = x + scalar_norm(y, t[p + "norm2b"], eps)
         if layers_out is not None:
             layers_out.append(x.copy())
