@@ -260,10 +260,13 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 3 : 6) flash_paged_ke
 // out[row][head] = sum_z 2^(m_z - m*) o_z / sum_z 2^(m_z - m*) l_z   over the parts of a row.
 // sink: a number per head that joins the sum below the line as one more part without an output,
 // exp(sink) (a key that takes weight and has no value); null: none.
+// extra_o [rows][Hq][HD], extra_ml [rows][Hq][2]: one more part per row and head that lies in a
+// buffer of its own (what a row sees outside its window); null: none.
 template <int HD>
 __global__ void merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                              bf16* __restrict__ out, const int* __restrict__ rows, int Hq, int splits,
-                             float* __restrict__ clear, int clear_stride, const float* __restrict__ sink) {
+                             float* __restrict__ clear, int clear_stride, const float* __restrict__ sink,
+                             const float* __restrict__ extra_o, const float* __restrict__ extra_ml) {
   pdl_trigger();
   pdl_wait();
   const int row = rows ? rows[blockIdx.x] : (int)blockIdx.x;
@@ -275,8 +278,15 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
   const float sk = sink ? sink[blockIdx.y] * 1.4426950408889634f : -INFINITY;
   float mstar = sk;
   for (int z = 0; z < splits; ++z) mstar = fmaxf(mstar, part_ml[(rowhead * splits + z) * 2]);
+  const float me = extra_ml ? extra_ml[rowhead * 2] : -INFINITY;
+  mstar = fmaxf(mstar, me);
   for (int d = threadIdx.x; d < HD; d += blockDim.x) {
     float acc = 0.f, lsum = sink ? exp2f(sk - mstar) : 0.f;
+    if (me != -INFINITY) {
+      const float w = exp2f(me - mstar);
+      acc = w * extra_o[rowhead * HD + d];
+      lsum += w * extra_ml[rowhead * 2 + 1];
+    }
     for (int z = 0; z < splits; ++z) {
       const float mz = part_ml[(rowhead * splits + z) * 2];
       if (mz == -INFINITY) continue;      // a part without keys: what lies in its place is not read
@@ -346,15 +356,33 @@ LLM_EXPORT int llm_attention_flash(const void* q, void* out, float* part_o, floa
   return LLM_ERR_UNSUPPORTED;
 }
 
-// Merge of the parts of split keys, with an optional sink per head (float32 [Hq]) in the sum.
+// Merge of the parts of split keys, with an optional sink per head (float32 [Hq]) in the sum and an
+// optional further part per row and head (extra_o [all rows][Hq][hd], extra_ml [all rows][Hq][2]).
+LLM_EXPORT int llm_attention_merge_extra(const float* part_o, const float* part_ml, void* out, const int* rows,
+                                         int n_rows, int Hq, int hd, int splits, float* clear, int clear_stride,
+                                         const float* sink, const float* extra_o, const float* extra_ml,
+                                         cudaStream_t stream);
+
 LLM_EXPORT int llm_attention_merge_sink(const float* part_o, const float* part_ml, void* out, const int* rows,
                                         int n_rows, int Hq, int hd, int splits, float* clear, int clear_stride,
                                         const float* sink, cudaStream_t stream) {
+  return llm_attention_merge_extra(part_o, part_ml, out, rows, n_rows, Hq, hd, splits, clear, clear_stride, sink,
+                                   nullptr, nullptr, stream);
+}
+
+LLM_EXPORT int llm_attention_merge_extra(const float* part_o, const float* part_ml, void* out, const int* rows,
+                                         int n_rows, int Hq, int hd, int splits, float* clear, int clear_stride,
+                                         const float* sink, const float* extra_o, const float* extra_ml,
+                                         cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   dim3 grid(n_rows, Hq);
-  if (hd == 128) return launch_pdl(merge_kernel<128>, grid, 128, 0, stream, part_o, part_ml, (bf16*)out, rows, Hq, splits, clear, clear_stride, sink);
-  if (hd == 64) return launch_pdl(merge_kernel<64>, grid, 64, 0, stream, part_o, part_ml, (bf16*)out, rows, Hq, splits, clear, clear_stride, sink);
-  if (hd == 32) return launch_pdl(merge_kernel<32>, grid, 32, 0, stream, part_o, part_ml, (bf16*)out, rows, Hq, splits, clear, clear_stride, sink);
+#define MERGE(HD)                                                                                             \
+  return launch_pdl(merge_kernel<HD>, grid, HD, 0, stream, part_o, part_ml, (bf16*)out, rows, Hq, splits, clear, \
+                    clear_stride, sink, extra_o, extra_ml)
+  if (hd == 128) MERGE(128);
+  if (hd == 64) MERGE(64);
+  if (hd == 32) MERGE(32);
+#undef MERGE
   return LLM_ERR_UNSUPPORTED;
 }
 

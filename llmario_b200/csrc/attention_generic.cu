@@ -55,13 +55,17 @@ struct PooledSource {
 
 // VEC: the head size is a multiple of 8, so a key row is read in 16-byte (32-byte) pieces.
 // NACC: 32-channel pieces of a value row that a lane sums (vd <= 32 * NACC)
-template <typename T, bool VEC, int NACC>
+// EXTRAS: only what lies outside the window (pooled blocks, kept first keys, the sink) is summed,
+// and the result is left as a part for a merge with the window's keys, which another kernel sums:
+// part_o [rows][Hq][hd] the weighted values without the division, part_ml [rows][Hq][2] the
+// maximum as a base-2 logarithm (score times log2 e) and the sum of the weights.
+template <typename T, bool VEC, int NACC, bool EXTRAS>
 __global__ void __launch_bounds__(WARPS * 32) attention_generic_kernel(
     const T* __restrict__ q, T* __restrict__ out, const T* __restrict__ k_cache,
     const T* __restrict__ v_cache, long long page_stride, const int* __restrict__ block_table,
     int table_stride, const int* __restrict__ row_slot, const int* __restrict__ row_pos, int rows,
     int Hq, int Hkv, int hd, int page_size, float scale, int window, const float* __restrict__ sink, int vd,
-    int keep_first, const PooledSource pooled) {
+    int keep_first, const PooledSource pooled, float* __restrict__ part_o, float* __restrict__ part_ml) {
   __shared__ float q_s[WARPS][MAX_HD];
   const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * WARPS + warp_in_block;
@@ -146,6 +150,27 @@ __global__ void __launch_bounds__(WARPS * 32) attention_generic_kernel(
       off = (long long)table[p / page_size] * page_stride + ((long long)kvh * page_size + p % page_size) * hd;
     tile(valid, k_cache, v_cache, off);
   }
+  if (EXTRAS) {
+    if (sink) {      // the sink is one more entry of this part
+      const float m_new = fmaxf(m, sink[h]);
+      const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+      l = l * corr + expf(sink[h] - m_new);
+#pragma unroll
+      for (int i = 0; i < NACC; ++i) acc[i] *= corr;
+      m = m_new;
+    }
+    float* po = part_o + ((size_t)t * Hq + h) * hd;
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) {
+      const int d = lane + 32 * i;
+      if (d < hd) po[d] = d < vd ? acc[i] : 0.f;
+    }
+    if (lane == 0) {
+      part_ml[((size_t)t * Hq + h) * 2] = m * 1.4426950408889634f;
+      part_ml[((size_t)t * Hq + h) * 2 + 1] = l;
+    }
+    return;
+  }
   for (int base = (lo / 32) * 32; base <= pos; base += 32) {
     const int p = base + lane;
     const bool valid = p >= lo && p <= pos;
@@ -188,10 +213,10 @@ LLM_EXPORT int llm_attention_generic_ext(const void* q, void* out, const void* k
   const long long items = (long long)rows * Hq;
   const int blocks = (int)((items + WARPS - 1) / WARPS);
 #define GENERIC(T, V, N)                                                                            \
-  attention_generic_kernel<T, V, N><<<blocks, WARPS * 32, 0, stream>>>(                             \
+  attention_generic_kernel<T, V, N, false><<<blocks, WARPS * 32, 0, stream>>>(                      \
       (const T*)q, (T*)out, (const T*)k_cache, (const T*)v_cache, page_stride, block_table,         \
       table_stride, row_slot, row_pos, rows, Hq, Hkv, hd, page_size, scale, window, sink, vd,       \
-      keep_first, pooled)
+      keep_first, pooled, nullptr, nullptr)
 #define GENERIC_N(T, V)                                  \
   do {                                                   \
     if (vd <= 128) GENERIC(T, V, 4);                     \
@@ -219,4 +244,37 @@ LLM_EXPORT int llm_attention_generic(const void* q, void* out, const void* k_cac
   return llm_attention_generic_ext(q, out, k_cache, v_cache, dtype, page_stride, block_table, table_stride,
                                    row_slot, row_pos, rows, Hq, Hkv, hd, page_size, scale, window, sink, vd, 0,
                                    nullptr, nullptr, 0, nullptr, 0, 0, stream);
+}
+
+// Only what a row sees outside its window: the pooled blocks that lie behind it, the kept first
+// keys that it has passed, and the sink, as one part for a merge with the window's keys (which the
+// tensor-core kernels sum).  bfloat16 caches with head sizes up to 128 that are multiples of 8.
+LLM_EXPORT int llm_attention_extras(const void* q, float* part_o, float* part_ml, const void* k_cache,
+                                    const void* v_cache, long long page_stride, const int* block_table,
+                                    int table_stride, const int* row_slot, const int* row_pos, int rows, int Hq,
+                                    int Hkv, int hd, int page_size, float scale, int window, const float* sink,
+                                    int keep_first, const void* pk_cache, const void* pv_cache,
+                                    long long p_page_stride, const int* p_table, int p_table_stride, int pool,
+                                    cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (hd > 128 || hd <= 0 || hd % 8 || Hkv <= 0 || Hq % Hkv != 0 || window <= 0) return LLM_ERR_UNSUPPORTED;
+  if (keep_first < 0 || !part_o || !part_ml || (pk_cache != nullptr && (pool <= 0 || !pv_cache || !p_table)))
+    return LLM_ERR_ARGUMENT;
+  PooledSource pooled;
+  pooled.k = pk_cache, pooled.v = pv_cache, pooled.page_stride = p_page_stride, pooled.table = p_table;
+  pooled.table_stride = p_table_stride, pooled.pool = pool;
+  const bool vec = (page_stride % 8) == 0 && (((uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0 &&
+                   (pk_cache == nullptr ||
+                    ((p_page_stride % 8) == 0 && (((uintptr_t)pk_cache | (uintptr_t)pv_cache) & 15) == 0));
+  const long long items = (long long)rows * Hq;
+  const int blocks = (int)((items + WARPS - 1) / WARPS);
+#define EXTRAS_GO(V)                                                                                          \
+  attention_generic_kernel<bf16, V, 4, true><<<blocks, WARPS * 32, 0, stream>>>(                              \
+      (const bf16*)q, nullptr, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, block_table,          \
+      table_stride, row_slot, row_pos, rows, Hq, Hkv, hd, page_size, scale, window, sink, hd, keep_first,     \
+      pooled, part_o, part_ml)
+  if (vec) EXTRAS_GO(true);
+  else EXTRAS_GO(false);
+#undef EXTRAS_GO
+  return launch_status();
 }

@@ -57,7 +57,8 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
     long long rows_per_page, int v_row_off, const bf16* __restrict__ k_cache,
     const bf16* __restrict__ v_cache, long long page_stride, bf16* __restrict__ out, const int* __restrict__ block_table, int table_stride,
     const int* __restrict__ items, int Hq, int Hkv, int page_size, float scale_log2, int window,
-    int* __restrict__ status, const float* __restrict__ sink) {
+    int* __restrict__ status, const float* __restrict__ sink, const float* __restrict__ extra_o,
+    const float* __restrict__ extra_ml) {
   constexpr int HALVES = HD / 64;
   constexpr uint32_t S_COLS = KT;              // fp32 scores of a tile
   constexpr uint32_t O_COL = 2 * S_COLS;       // first column of the output accumulator
@@ -406,23 +407,49 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_kernel(
       // a sink joins the sum as exp(sink): one more key that has no value (m_used is a base-2
       // logarithm, and finite for a row that sees its own key)
       if (sink && rvalid) l += ex2(sink[head] * 1.4426950408889634f - m_used);
+      // one more part of the row's softmax from a buffer: what the row sees outside its window
+      float wa = 1.0f, wb = 0.f;
+      const float* eo = nullptr;
+      if (extra_ml && rvalid) {
+        const size_t rowhead = (size_t)(it.row_start + tok) * Hq + head;
+        const float me = extra_ml[rowhead * 2];
+        if (me != -INFINITY) {
+          const float mm = fmaxf(m_used, me);
+          wa = ex2(m_used - mm), wb = ex2(me - mm);
+          l = l * wa + extra_ml[rowhead * 2 + 1] * wb;
+          eo = extra_o + rowhead * HD + oc0;
+        }
+      }
       if (done) {
         tc_fence_after();
-        const float inv = 1.0f / l;
+        const float inv = wa / l;
+        wb /= l;
         bf16* dst = out + ((size_t)(it.row_start + tok) * Hq + head) * HD + oc0;
 #pragma unroll 1
         for (int c = 0; c < OC; c += 32) {
           uint32_t w[32];
           tmem_ld32(tmem + lane_base + O_COL + oc0 + c, w);
           tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(__uint_as_float(w[i]) * inv);
+          if (eo) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              const float4 e = *reinterpret_cast<const float4*>(eo + c + i);
+              w[i] = __float_as_uint(fmaf(e.x, wb, __uint_as_float(w[i])));
+              w[i + 1] = __float_as_uint(fmaf(e.y, wb, __uint_as_float(w[i + 1])));
+              w[i + 2] = __float_as_uint(fmaf(e.z, wb, __uint_as_float(w[i + 2])));
+              w[i + 3] = __float_as_uint(fmaf(e.w, wb, __uint_as_float(w[i + 3])));
+            }
+          }
           if (rvalid) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
               uint4 u;
-              u.x = pack2(__uint_as_float(w[i]) * inv, __uint_as_float(w[i + 1]) * inv);
-              u.y = pack2(__uint_as_float(w[i + 2]) * inv, __uint_as_float(w[i + 3]) * inv);
-              u.z = pack2(__uint_as_float(w[i + 4]) * inv, __uint_as_float(w[i + 5]) * inv);
-              u.w = pack2(__uint_as_float(w[i + 6]) * inv, __uint_as_float(w[i + 7]) * inv);
+              u.x = pack2(__uint_as_float(w[i]), __uint_as_float(w[i + 1]));
+              u.y = pack2(__uint_as_float(w[i + 2]), __uint_as_float(w[i + 3]));
+              u.z = pack2(__uint_as_float(w[i + 4]), __uint_as_float(w[i + 5]));
+              u.w = pack2(__uint_as_float(w[i + 6]), __uint_as_float(w[i + 7]));
               *reinterpret_cast<uint4*>(dst + c + i) = u;
             }
           }
@@ -476,7 +503,8 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_persistent_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
     long long rows_per_page, int v_row_off, bf16* __restrict__ out, const int* __restrict__ block_table,
     int table_stride, const int* __restrict__ items, int n_items, int Hq, int Hkv, int page_size,
-    float scale_log2, int window, int* __restrict__ status, const float* __restrict__ sink) {
+    float scale_log2, int window, int* __restrict__ status, const float* __restrict__ sink,
+    const float* __restrict__ extra_o, const float* __restrict__ extra_ml) {
   constexpr int HALVES = HD / 64;
   constexpr uint32_t S_COLS = KT;
   constexpr uint32_t O_COL = 2 * S_COLS;
@@ -756,7 +784,21 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_persistent_kernel(
       tmem_ld_wait();
       l += __uint_as_float(other);
       if (sink && rvalid) l += ex2(sink[head] * 1.4426950408889634f - m_used);
-      const float inv = 1.0f / l;
+      // one more part of the row's softmax from a buffer: what the row sees outside its window
+      float wa = 1.0f, wb = 0.f;
+      const float* eo = nullptr;
+      if (extra_ml && rvalid) {
+        const size_t rowhead = (size_t)(w.it.row_start + tok) * Hq + head;
+        const float me = extra_ml[rowhead * 2];
+        if (me != -INFINITY) {
+          const float mm = fmaxf(m_used, me);
+          wa = ex2(m_used - mm), wb = ex2(me - mm);
+          l = l * wa + extra_ml[rowhead * 2 + 1] * wb;
+          eo = extra_o + rowhead * HD + oc0;
+        }
+      }
+      const float inv = wa / l;
+      wb /= l;
       bf16* dst = out + ((size_t)(w.it.row_start + tok) * Hq + head) * HD + oc0;
       // the whole half row into registers, so that the next item's first P V need not wait for
       // the stores
@@ -769,12 +811,24 @@ __global__ void __launch_bounds__(320, 1) attention_tcgen05_persistent_kernel(
       if (lane == 0) mbar_arrive(&sm.o_free);
       if (rvalid && done) {
 #pragma unroll
+        for (int i = 0; i < OC; ++i) u[i] = __float_as_uint(__uint_as_float(u[i]) * inv);
+        if (eo) {
+#pragma unroll
+          for (int i = 0; i < OC; i += 4) {
+            const float4 e = *reinterpret_cast<const float4*>(eo + i);
+            u[i] = __float_as_uint(fmaf(e.x, wb, __uint_as_float(u[i])));
+            u[i + 1] = __float_as_uint(fmaf(e.y, wb, __uint_as_float(u[i + 1])));
+            u[i + 2] = __float_as_uint(fmaf(e.z, wb, __uint_as_float(u[i + 2])));
+            u[i + 3] = __float_as_uint(fmaf(e.w, wb, __uint_as_float(u[i + 3])));
+          }
+        }
+#pragma unroll
         for (int i = 0; i < OC; i += 8) {
           uint4 pk4;
-          pk4.x = pack2(__uint_as_float(u[i]) * inv, __uint_as_float(u[i + 1]) * inv);
-          pk4.y = pack2(__uint_as_float(u[i + 2]) * inv, __uint_as_float(u[i + 3]) * inv);
-          pk4.z = pack2(__uint_as_float(u[i + 4]) * inv, __uint_as_float(u[i + 5]) * inv);
-          pk4.w = pack2(__uint_as_float(u[i + 6]) * inv, __uint_as_float(u[i + 7]) * inv);
+          pk4.x = pack2(__uint_as_float(u[i]), __uint_as_float(u[i + 1]));
+          pk4.y = pack2(__uint_as_float(u[i + 2]), __uint_as_float(u[i + 3]));
+          pk4.z = pack2(__uint_as_float(u[i + 4]), __uint_as_float(u[i + 5]));
+          pk4.w = pack2(__uint_as_float(u[i + 6]), __uint_as_float(u[i + 7]));
           *reinterpret_cast<uint4*>(dst + i) = pk4;
         }
       }
@@ -818,7 +872,8 @@ template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mkv, int tma_kv, long long rows_per_page, int v_row_off,
            const bf16* kc, const bf16* vc, long long page_stride, bf16* out,
            const int* table, int table_stride, const int* items, int n_items, int Hq, int Hkv, int page_size,
-           float scale, int window, int persistent, int* status, const float* sink, cudaStream_t s) {
+           float scale, int window, int persistent, int* status, const float* sink, const float* extra_o,
+           const float* extra_ml, cudaStream_t s) {
   constexpr int smem = (int)sizeof(AttnStorage<HD>) + 1024;
   static_assert(smem <= 227 * 1024, "the Q tile and three stages of K and V fit one SM");
   if (tma_kv && persistent) {
@@ -839,7 +894,8 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, int tma_kv, long long 
         pconf = true;
       }
       return launch_pdl(pk, dim3(sms), 320, smem, s, mq, mkv, rows_per_page, v_row_off, out, table, table_stride,
-                        items, n_items, Hq, Hkv, page_size, scale * 1.4426950408889634f, window, status, sink);
+                        items, n_items, Hq, Hkv, page_size, scale * 1.4426950408889634f, window, status, sink, extra_o,
+                        extra_ml);
     }
   }
   // keys and values by TMA leave warps 6-9 free: they take half of every row's softmax
@@ -852,7 +908,8 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, int tma_kv, long long 
   }
   dim3 grid(n_items, Hkv);
   return launch_pdl(kernel, grid, 320, smem, s, mq, mkv, tma_kv, rows_per_page, v_row_off, kc, vc, page_stride, out,
-                    table, table_stride, items, Hq, Hkv, page_size, scale * 1.4426950408889634f, window, status, sink);
+                    table, table_stride, items, Hq, Hkv, page_size, scale * 1.4426950408889634f, window, status, sink,
+                    extra_o, extra_ml);
 }
 }  // namespace
 
@@ -864,12 +921,23 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, int tma_kv, long long 
 // persistent: non-zero lets the kernel run, when K and V come by TMA and there are more (item, KV
 // head) pairs than SMs, as one CTA per SM that walks its share of the pairs; that pays while the
 // items are short (it saves about 3 us per pair) and costs a few percent when they are long.
+LLM_EXPORT int llm_attention_tcgen05_extra(const void* q, void* out, int rows, const void* k_cache,
+                                           const void* v_cache, long long page_stride, long long n_pages,
+                                           const int* block_table, int table_stride, const int* items,
+                                           int n_items, int Hq, int Hkv, int hd, int page_size, float scale,
+                                           int window, int persistent, int* status, const float* sink,
+                                           const float* extra_o, const float* extra_ml, cudaStream_t stream);
+
 LLM_EXPORT int llm_attention_tcgen05_sink(const void* q, void* out, int rows, const void* k_cache,
                                           const void* v_cache, long long page_stride, long long n_pages,
                                           const int* block_table, int table_stride, const int* items,
                                           int n_items, int Hq, int Hkv, int hd, int page_size, float scale,
                                           int window, int persistent, int* status, const float* sink,
-                                          cudaStream_t stream);
+                                          cudaStream_t stream) {
+  return llm_attention_tcgen05_extra(q, out, rows, k_cache, v_cache, page_stride, n_pages, block_table,
+                                     table_stride, items, n_items, Hq, Hkv, hd, page_size, scale, window,
+                                     persistent, status, sink, nullptr, nullptr, stream);
+}
 
 LLM_EXPORT int llm_attention_tcgen05(const void* q, void* out, int rows, const void* k_cache,
                                      const void* v_cache, long long page_stride, long long n_pages,
@@ -882,13 +950,17 @@ LLM_EXPORT int llm_attention_tcgen05(const void* q, void* out, int rows, const v
                                     persistent, status, nullptr, stream);
 }
 
-// The same with a sink per query head (float32 [Hq], or null) in every row's softmax sum.
-LLM_EXPORT int llm_attention_tcgen05_sink(const void* q, void* out, int rows, const void* k_cache,
-                                          const void* v_cache, long long page_stride, long long n_pages,
-                                          const int* block_table, int table_stride, const int* items,
-                                          int n_items, int Hq, int Hkv, int hd, int page_size, float scale,
-                                          int window, int persistent, int* status, const float* sink,
-                                          cudaStream_t stream) {
+// The same with a sink per query head (float32 [Hq], or null) in every row's softmax sum, and with
+// one more part of every row's softmax from buffers (extra_o [rows][Hq][hd] weighted values without
+// the division, extra_ml [rows][Hq][2] maximum as a base-2 logarithm and sum of weights; or null):
+// what a row sees outside the one range of keys that this kernel walks.
+LLM_EXPORT int llm_attention_tcgen05_extra(const void* q, void* out, int rows, const void* k_cache,
+                                           const void* v_cache, long long page_stride, long long n_pages,
+                                           const int* block_table, int table_stride, const int* items,
+                                           int n_items, int Hq, int Hkv, int hd, int page_size, float scale,
+                                           int window, int persistent, int* status, const float* sink,
+                                           const float* extra_o, const float* extra_ml, cudaStream_t stream) {
+  if ((extra_o == nullptr) != (extra_ml == nullptr) || ((uintptr_t)extra_o & 15)) return LLM_ERR_ARGUMENT;
   if (n_items <= 0) return 0;
   if (Hkv <= 0 || Hq % Hkv) return LLM_ERR_ARGUMENT;
   const int G = Hq / Hkv;
@@ -913,8 +985,8 @@ LLM_EXPORT int llm_attention_tcgen05_sink(const void* q, void* out, int rows, co
   if (hd == 128)
     return launch<128>(mq, mkv, tma_kv, rows_per_page, v_row_off, (const bf16*)k_cache, (const bf16*)v_cache,
                        page_stride, (bf16*)out, block_table, table_stride, items, n_items, Hq, Hkv, page_size, scale,
-                       window, persistent, status, sink, stream);
+                       window, persistent, status, sink, extra_o, extra_ml, stream);
   return launch<64>(mq, mkv, tma_kv, rows_per_page, v_row_off, (const bf16*)k_cache, (const bf16*)v_cache,
                     page_stride, (bf16*)out, block_table, table_stride, items, n_items, Hq, Hkv, page_size, scale,
-                    window, persistent, status, sink, stream);
+                    window, persistent, status, sink, extra_o, extra_ml, stream);
 }

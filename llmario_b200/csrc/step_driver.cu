@@ -99,6 +99,20 @@ int llm_attention_tcgen05_sink(const void* q, void* out, int rows, const void* k
 int llm_attention_merge_sink(const float* part_o, const float* part_ml, void* out, const int* rows, int n_rows,
                              int Hq, int hd, int splits, float* clear, int clear_stride, const float* sink,
                              cudaStream_t stream);
+int llm_attention_merge_extra(const float* part_o, const float* part_ml, void* out, const int* rows, int n_rows,
+                              int Hq, int hd, int splits, float* clear, int clear_stride, const float* sink,
+                              const float* extra_o, const float* extra_ml, cudaStream_t stream);
+int llm_attention_tcgen05_extra(const void* q, void* out, int rows, const void* k_cache, const void* v_cache,
+                                long long page_stride, long long n_pages, const int* block_table, int table_stride,
+                                const int* items, int n_items, int Hq, int Hkv, int hd, int page_size, float scale,
+                                int window, int persistent, int* status, const float* sink, const float* extra_o,
+                                const float* extra_ml, cudaStream_t stream);
+int llm_attention_extras(const void* q, float* part_o, float* part_ml, const void* k_cache, const void* v_cache,
+                         long long page_stride, const int* block_table, int table_stride, const int* row_slot,
+                         const int* row_pos, int rows, int Hq, int Hkv, int hd, int page_size, float scale,
+                         int window, const float* sink, int keep_first, const void* pk_cache, const void* pv_cache,
+                         long long p_page_stride, const int* p_table, int p_table_stride, int pool,
+                         cudaStream_t stream);
 int llm_kv_gather(const void* k_src, const void* v_src, long long src_page_stride, const int* block_table,
                   int table_stride, int page_size, void* k_dst, void* v_dst, long long dst_page_stride,
                   int dst_page_size, int Hkv, int hd, int dtype, const int* items, int n_items,
@@ -151,7 +165,7 @@ int g_fuse_mode = 0;                        // 0: when few waves, 1: always, 2: 
 enum Kind : int {
   K_NORM, K_GEMM_TCGEN05, K_GEMM_SIMT, K_ROPE_TABLE, K_ROPE_STORE, K_DECODE_FUSED, K_DECODE_TMA, K_DECODE,
   K_FLASH, K_MERGE, K_TCGEN05, K_TCGEN05_X2, K_GENERIC, K_SILU_MUL, K_KV_GATHER, K_DECODE_PERSISTENT,
-  N_KINDS
+  K_EXTRAS, N_KINDS
 };
 long long g_counts[N_KINDS] = {};
 
@@ -180,7 +194,7 @@ bool tc_ok(const void* a, int a_dt, int lda, const void* w, int w_dt, int ldw, i
 // ------------------------------------------------------------------------------------------------
 enum BufId : int {
   B_H = 1, B_PROJ, B_ZPROJ /* + width */, B_Q, B_OUT, B_ACT, B_GATE_UP, B_PART_O, B_PART_ML, B_ROPE /* + k */,
-  B_ITEMS, B_GATHER
+  B_ITEMS, B_GATHER, B_EXTRA_O, B_EXTRA_ML
 };
 
 struct Buf { void* p = nullptr; size_t bytes = 0; bool kept_zero = false; };
@@ -525,23 +539,45 @@ struct Run {
     const bool whole_values = L.value_dim == 0 || L.value_dim == hd;
     const int ps = c.page_size;
     const bool tc = (hd == 64 || hd == 128) && 128 % group == 0 && (c.page_stride * 2) % 16 == 0;
-    // kept first keys and pooled blocks make a row's visible keys more than one range: the
-    // generic kernel walks them, the others know one range
-    if (L.keep_first > 0 || L.pool > 0)
+    // Kept first keys and pooled blocks make a row's visible keys more than one range.  The generic
+    // kernel walks them all; the tensor-core kernels know one range, so for them a kernel of its
+    // own sums what lies outside the window (with the sink) into one part per row and head, and
+    // the kernels of the window take that part into their last step (long items) or their merge
+    // (short ones).
+    const bool outside = L.keep_first > 0 || L.pool > 0;
+    const bool plain = !whole_values || st.dtype != LLM_BF16 || !(hd == 32 || hd == 64 || hd == 128) || group > 16;
+    if (outside && (plain || !tc || window <= 0))
       return check(llm_attention_generic_ext(q, out, c.k, c.v, st.dtype, c.page_stride, c.block_table,
                                              c.table_stride, st.row_slot, st.row_pos, st.rows, Hq, Hkv, hd,
                                              c.page_size, L.scale, window, L.sink, L.value_dim, L.keep_first,
                                              L.pool > 0 ? L.pool_k : nullptr, L.pool_v, L.pool_page_stride,
                                              L.pool_table, L.pool_table_stride, L.pool, stream), K_GENERIC);
-    if (!whole_values || st.dtype != LLM_BF16 || !(hd == 32 || hd == 64 || hd == 128) || group > 16 ||
-        (L.sink != nullptr && !tc))
+    if (plain || (L.sink != nullptr && !tc))
       return check(llm_attention_generic(q, out, c.k, c.v, st.dtype, c.page_stride, c.block_table,
                                          c.table_stride, st.row_slot, st.row_pos, st.rows, Hq, Hkv, hd,
                                          c.page_size, L.scale, window, L.sink, L.value_dim, stream), K_GENERIC);
-    const bool x2 = tc && L.sink == nullptr && ps >= 32 && (ps & (ps - 1)) == 0 && c.storage != nullptr && ps < 64 &&
+    const float* sink = L.sink;
+    float *extra_o = nullptr, *extra_ml = nullptr;
+    if (outside) {
+      void *o = nullptr, *ml = nullptr;
+      int rc = buffer(B_EXTRA_O, (size_t)st.rows * Hq * hd * sizeof(float), &o);
+      if (rc) return rc;
+      rc = buffer(B_EXTRA_ML, (size_t)st.rows * Hq * 2 * sizeof(float), &ml);
+      if (rc) return rc;
+      extra_o = (float*)o, extra_ml = (float*)ml;
+      rc = check(llm_attention_extras(q, extra_o, extra_ml, c.k, c.v, c.page_stride, c.block_table, c.table_stride,
+                                      st.row_slot, st.row_pos, st.rows, Hq, Hkv, hd, c.page_size, L.scale, window,
+                                      L.sink, L.keep_first, L.pool > 0 ? L.pool_k : nullptr, L.pool_v,
+                                      L.pool_page_stride, L.pool_table, L.pool_table_stride, L.pool, stream),
+                 K_EXTRAS);
+      if (rc) return rc;
+      sink = nullptr;      // it is in the part
+    }
+    const bool merged = sink != nullptr || outside;      // short items always end in a merge
+    const bool x2 = tc && !merged && ps >= 32 && (ps & (ps - 1)) == 0 && c.storage != nullptr && ps < 64 &&
                     (long long)st.rows * Hkv >= 4LL * sm_count() * (128 / group);
     const Plan* plan = nullptr;
-    int rc = plan_for(group, (x2 ? 256 : tc ? 128 : 64) / group, &plan, L.sink != nullptr);
+    int rc = plan_for(group, (x2 ? 256 : tc ? 128 : 64) / group, &plan, merged);
     if (rc) return rc;
     const int reach = reach_of(window, st.max_pos);
     if (plan->n_small) {
@@ -550,10 +586,10 @@ struct Run {
                        ? llm_decode_splits(plan->n_small, Hkv, reach, (tma ? DECODE_TMA_CTAS_PER_SM : 6) * sm_count(),
                                            tma ? DECODE_TMA_TILE : 32)
                        : 1;
-      if (L.sink != nullptr && splits < 2) splits = 2;      // the sink joins the sum in the merge
+      if (merged && splits < 2) splits = 2;      // the sink and the outside part join in the merge
       float *part_o, *part_ml;
       const int resident = DECODE_TMA_CTAS_PER_SM * sm_count();
-      if (g_persistent_decode && L.sink == nullptr && tma && plan->small == nullptr && st.rows <= PERSISTENT_MAX_ROWS &&
+      if (g_persistent_decode && !merged && tma && plan->small == nullptr && st.rows <= PERSISTENT_MAX_ROWS &&
           (long long)plan->n_small * Hkv * splits > resident &&
           (long long)plan->n_small * Hkv * splits <= (long long)PERSISTENT_MAX_WAVES * resident) {
         rc = parts(PERSISTENT_PARTS, L, &part_o, &part_ml);
@@ -584,8 +620,8 @@ struct Run {
                                        16, Hq, Hkv, hd, ps, L.scale, window, splits, stream), K_FLASH);
       if (rc) return rc;
       if (splits > 1) {
-        rc = check(llm_attention_merge_sink(part_o, part_ml, out, plan->small_rows, plan->n_small, Hq, hd,
-                                            splits, nullptr, 0, L.sink, stream), K_MERGE);
+        rc = check(llm_attention_merge_extra(part_o, part_ml, out, plan->small_rows, plan->n_small, Hq, hd,
+                                             splits, nullptr, 0, sink, extra_o, extra_ml, stream), K_MERGE);
         if (rc) return rc;
       }
     }
@@ -614,19 +650,20 @@ struct Run {
                                    Hkv, hd, LLM_BF16, gp->list, gp->n_requests, gp->total_chunks, stream),
                      K_KV_GATHER);
           if (rc) return rc;
-          rc = check(llm_attention_tcgen05_sink(q, out, st.rows, ks, vs, stride, gp->scratch_pages, gp->table,
-                                                gp->table_stride, gp->gathered, gp->n_gathered, Hq, Hkv, hd, D, L.scale,
-                                                window, persistent, st.status, L.sink, stream), K_TCGEN05);
+          rc = check(llm_attention_tcgen05_extra(q, out, st.rows, ks, vs, stride, gp->scratch_pages, gp->table,
+                                                 gp->table_stride, gp->gathered, gp->n_gathered, Hq, Hkv, hd, D,
+                                                 L.scale, window, persistent, st.status, sink, extra_o, extra_ml,
+                                                 stream), K_TCGEN05);
           if (rc) return rc;
           direct = gp->direct;
           n_direct = gp->n_direct;
         }
       }
       if (n_direct == 0) return 0;
-      return check(llm_attention_tcgen05_sink(q, out, st.rows, c.k, c.v, c.page_stride,
-                                              c.storage != nullptr ? c.n_pages : 0, c.block_table, c.table_stride,
-                                              direct, n_direct, Hq, Hkv, hd, ps, L.scale, window, persistent,
-                                              st.status, L.sink, stream), K_TCGEN05);
+      return check(llm_attention_tcgen05_extra(q, out, st.rows, c.k, c.v, c.page_stride,
+                                               c.storage != nullptr ? c.n_pages : 0, c.block_table, c.table_stride,
+                                               direct, n_direct, Hq, Hkv, hd, ps, L.scale, window, persistent,
+                                               st.status, sink, extra_o, extra_ml, stream), K_TCGEN05);
     }
     if (plan->n_large)
       return check(llm_attention_flash(q, out, nullptr, nullptr, c.k, c.v, c.page_stride, c.block_table,

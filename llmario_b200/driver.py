@@ -93,7 +93,7 @@ def arena_drop() -> None:
 
 KINDS = ("norm", "gemm_tcgen05", "gemm_simt", "rope_table", "rope_store", "decode_fused",
          "decode_tma", "decode", "flash", "merge", "tcgen05", "tcgen05_x2", "generic", "silu_mul",
-         "kv_gather", "decode_persistent")
+         "kv_gather", "decode_persistent", "outside_window")
 
 
 def kernel_counts() -> Dict[str, int]:

@@ -447,7 +447,7 @@ NEEDLE_CHANNEL = 20      # of head 0; behind the rotated channels
 NEEDLE_KEEP, NEEDLE_POOL = 3, 4
 
 
-def needle_model(kind: str, window: int) -> str:
+def needle_model(kind: str, window: int, dim: int = 32) -> str:
     """One layer whose weights make one score stand out.  Token 0 is the needle: its embedding is
     large in coordinate 0, which only one key channel reads; token 1 is the probe, large in
     coordinate 1, which only the same query channel reads; the norms' weights of that channel
@@ -455,16 +455,17 @@ def needle_model(kind: str, window: int) -> str:
     needle (as a token, as a kept first token, or inside a pooled block), and an edge that is
     off by one shows as a large error.  The sinks are large enough to take visible weight.
     ``kind``: "needle_attn" (kept-window attention) or "needle_par" (pooled window attention
-    beside a recurrence)."""
-    name = f"{kind}{window}"
+    beside a recurrence).  ``dim``: the head size (64 is one that the tensor-core kernels have, so
+    in bfloat16 the keys outside the window are summed by a kernel of their own)."""
+    name = f"{kind}{window}_{dim}"
     if name in CONFIGS:
         return name
     if kind == "needle_attn":
-        CONFIGS[name] = config([attention(heads=2, kv_heads=1, dim=32, vdim=32, size=window,
+        CONFIGS[name] = config([attention(heads=2, kv_heads=1, dim=dim, vdim=dim, size=window,
                                           keep=NEEDLE_KEEP)], width=64, vocab=64)
         x = "l0.mix."
     else:
-        CONFIGS[name] = config([parallel(width=16, heads=2, kv_heads=1, dim=32, vdim=32, conv=3,
+        CONFIGS[name] = config([parallel(width=16, heads=2, kv_heads=1, dim=dim, vdim=dim, conv=3,
                                          size=window, pool=NEEDLE_POOL, rot=8)], width=64, vocab=64)
         x = "l0.mix.left."
     w = {n: a.copy() for n, a in _weights(CONFIGS[name], 7).items()}
@@ -512,15 +513,18 @@ def needle_tokens(window: int, n: int, seed: int = 3, start: int = 9):
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("kind", ("needle_attn", "needle_par"))
-@pytest.mark.parametrize("window,page", [(12, 16), (40, 16), (64, 64), (24, 32), (33, 8)])
-def test_a_key_that_stands_out_at_the_edges_of_windows(dtype, kind, window, page):
+@pytest.mark.parametrize("window,page,dim", [(12, 16, 32), (40, 16, 64), (64, 64, 32), (24, 32, 64),
+                                             (33, 8, 64), (64, 64, 64)])
+def test_a_key_that_stands_out_at_the_edges_of_windows(dtype, kind, window, page, dim):
     """Needles just inside and just outside the window of a probe, in a whole prompt, in
     portions whose cuts fall between needle and probe, and with the probes decoded one by one,
     over pages smaller than, equal to and larger than the window."""
-    name = needle_model(kind, window)
+    from llmario_b200 import driver
+    name = needle_model(kind, window, dim)
     n = 6 * window + 70
     toks, probes = needle_tokens(window, n)
     assert len(probes["just_inside"]) >= 2 and len(probes["just_outside"]) >= 2
+    before = driver.kernel_counts()["outside_window"]
     runner = runner_for(name, dtype, page_size=page, cache_tokens=1024)
     got = run_steps(runner, [[("a", toks, range(n))]])
     check_request(got["a"], name, toks, dtype, "needles, whole prompt")
@@ -531,17 +535,19 @@ def test_a_key_that_stands_out_at_the_edges_of_windows(dtype, kind, window, page
     steps = [[("b", toks[a:b], range(b - a))] for a, b in cuts] + [[("b", [t], [0])] for t in toks[at:]]
     got = run_steps(runner, steps)
     check_request(got["b"], name, toks, dtype, "needles, portions and single tokens")
+    if dtype == "bfloat16":     # which kernels summed what lies outside the window
+        assert (driver.kernel_counts()["outside_window"] > before) == (dim == 64)
 
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("page", (8, 64))
-def test_kept_first_tokens_far_away(dtype, page):
+@pytest.mark.parametrize("page,dim", ((8, 32), (64, 32), (8, 64), (32, 64)))
+def test_kept_first_tokens_far_away(dtype, page, dim):
     """A needle on the last kept position is seen by probes hundreds of tokens later, one on
     the next position is not: in a prompt, in portions and decoded, while the pages between go
     back to the pool."""
     window = 16
-    name = needle_model("needle_attn", window)
+    name = needle_model("needle_attn", window, dim)
     n = 300
     rng = np.random.default_rng(11)
     for needle_at in (NEEDLE_KEEP - 1, NEEDLE_KEEP, 0):
@@ -571,14 +577,14 @@ def test_kept_first_tokens_far_away(dtype, page):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("page", (8, 64))
-def test_pooled_blocks_just_seen_and_not_yet(dtype, page):
+@pytest.mark.parametrize("page,dim", ((8, 32), (64, 32), (16, 64), (64, 64)))
+def test_pooled_blocks_just_seen_and_not_yet(dtype, page, dim):
     """A needle inside a block: the probe on the first position that sees the block finds it
     (weakened by the mean), the probe one position earlier sees neither token nor block; probes
     hundreds of tokens later still find the block."""
     window = 20
     P = NEEDLE_POOL
-    name = needle_model("needle_par", window)
+    name = needle_model("needle_par", window, dim)
     n = 330
     rng = np.random.default_rng(12)
     toks = [int(t) for t in rng.integers(2, 64, n)]
