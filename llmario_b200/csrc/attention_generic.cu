@@ -188,6 +188,128 @@ __global__ void __launch_bounds__(WARPS * 32) attention_generic_kernel(
     if (d < vd) orow[d] = from_f32<T>(acc[i] * inv);
   }
 }
+
+// What lies outside the window for all heads of a group at once: one warp per (row, key head).
+// A lane scores one entry (a pooled block or a kept first key) against the GROUP queries that
+// share it, so a key row is read once for the group; the values are summed with a lane per pair
+// of channels.  Head sizes 64 and 128, bfloat16, 16-byte aligned rows.  The result is one part
+// per row and query head, as the EXTRAS form of the kernel above leaves it.
+template <int GROUP>
+__global__ void __launch_bounds__(WARPS * 32) attention_outside_kernel(
+    const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+    long long page_stride, const int* __restrict__ block_table, int table_stride, const int* __restrict__ row_slot,
+    const int* __restrict__ row_pos, int rows, int Hq, int Hkv, int hd, int page_size, float scale, int window,
+    const float* __restrict__ sink, int keep_first, const PooledSource pooled, float* __restrict__ part_o,
+    float* __restrict__ part_ml) {
+  __shared__ __align__(16) float q_s[WARPS][GROUP][128];
+  const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * WARPS + warp_in_block;
+  if (item >= (long long)rows * Hkv) return;
+  const int t = (int)(item / Hkv), kvh = (int)(item % Hkv);
+  const int pos = row_pos[t], slot = row_slot[t];
+  const int* table = block_table + (size_t)slot * table_stride;
+  const int behind = pos - window + 1 > 0 ? pos - window + 1 : 0;      // positions the window has passed
+  const int kept = keep_first < behind ? keep_first : behind;
+  const int seen = pooled.k != nullptr ? behind / pooled.pool : 0;     // blocks that lie wholly behind it
+  const int* ptable = pooled.k != nullptr ? pooled.table + (size_t)slot * pooled.table_stride : nullptr;
+  const int total = seen + kept;
+  const int pairs = hd / 64;      // pairs of channels per lane
+
+  float (*qs)[128] = q_s[warp_in_block];
+  const bf16* qrow = q + ((size_t)t * Hq + (size_t)kvh * GROUP) * hd;
+  for (int i = lane; i < GROUP * hd; i += 32) qs[i / hd][i % hd] = to_f32(qrow[i]);
+  __syncwarp();
+
+  float m[GROUP], l[GROUP], acc[GROUP][4];
+#pragma unroll
+  for (int g = 0; g < GROUP; ++g) {
+    m[g] = -INFINITY, l[g] = 0.f;
+    acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
+  }
+  for (int base = 0; base < total; base += 32) {
+    const int e = base + lane;
+    const bool valid = e < total;
+    const bf16 *kr = k_cache, *vr = v_cache;
+    if (valid) {
+      if (e < seen) {
+        const long long off = (long long)ptable[e / page_size] * pooled.page_stride +
+                              ((long long)kvh * page_size + e % page_size) * hd;
+        kr = (const bf16*)pooled.k + off, vr = (const bf16*)pooled.v + off;
+      } else {
+        const int p = e - seen;
+        const long long off = (long long)table[p / page_size] * page_stride +
+                              ((long long)kvh * page_size + p % page_size) * hd;
+        kr = k_cache + off, vr = v_cache + off;
+      }
+    }
+    float w[GROUP];
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g) w[g] = 0.f;
+    if (valid) {
+      for (int i = 0; i < hd; i += 8) {
+        Vec8<bf16> kv;
+        kv.load(kr + i);
+#pragma unroll
+        for (int g = 0; g < GROUP; ++g) {
+          const float4 a = *reinterpret_cast<const float4*>(&qs[g][i]);
+          const float4 b = *reinterpret_cast<const float4*>(&qs[g][i + 4]);
+          float d = w[g];
+          d = fmaf(a.x, kv.v[0], d), d = fmaf(a.y, kv.v[1], d), d = fmaf(a.z, kv.v[2], d), d = fmaf(a.w, kv.v[3], d);
+          d = fmaf(b.x, kv.v[4], d), d = fmaf(b.y, kv.v[5], d), d = fmaf(b.z, kv.v[6], d), d = fmaf(b.w, kv.v[7], d);
+          w[g] = d;
+        }
+      }
+    }
+    const unsigned mask = __ballot_sync(0xffffffffu, valid);
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g) {
+      const float sc = valid ? w[g] * scale : -INFINITY;
+      const float m_new = fmaxf(m[g], warp_max(sc));
+      w[g] = valid ? expf(sc - m_new) : 0.f;
+      const float corr = (m[g] == -INFINITY) ? 0.f : expf(m[g] - m_new);
+      l[g] = l[g] * corr + warp_sum(w[g]);
+      acc[g][0] *= corr, acc[g][1] *= corr, acc[g][2] *= corr, acc[g][3] *= corr;
+      m[g] = m_new;
+    }
+    for (int j = 0; j < 32; ++j) {
+      if (!((mask >> j) & 1u)) break;      // the entries of a tile are its first lanes
+      const bf16* vj = (const bf16*)__shfl_sync(0xffffffffu, (unsigned long long)vr, j);
+      float2 v0 = make_float2(0.f, 0.f), v1 = v0;
+      {
+        const uint32_t u = *reinterpret_cast<const uint32_t*>(vj + 2 * lane);
+        v0 = make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+      }
+      if (pairs > 1) {
+        const uint32_t u = *reinterpret_cast<const uint32_t*>(vj + 64 + 2 * lane);
+        v1 = make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+      }
+#pragma unroll
+      for (int g = 0; g < GROUP; ++g) {
+        const float wj = __shfl_sync(0xffffffffu, w[g], j);
+        acc[g][0] = fmaf(wj, v0.x, acc[g][0]), acc[g][1] = fmaf(wj, v0.y, acc[g][1]);
+        acc[g][2] = fmaf(wj, v1.x, acc[g][2]), acc[g][3] = fmaf(wj, v1.y, acc[g][3]);
+      }
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < GROUP; ++g) {
+    const int h = kvh * GROUP + g;
+    float mg = m[g], lg = l[g], corr = 1.f;
+    if (sink) {      // the sink is one more entry of this part
+      const float m_new = fmaxf(mg, sink[h]);
+      corr = (mg == -INFINITY) ? 0.f : expf(mg - m_new);
+      lg = lg * corr + expf(sink[h] - m_new);
+      mg = m_new;
+    }
+    float* po = part_o + ((size_t)t * Hq + h) * hd;
+    *reinterpret_cast<float2*>(po + 2 * lane) = make_float2(acc[g][0] * corr, acc[g][1] * corr);
+    if (pairs > 1) *reinterpret_cast<float2*>(po + 64 + 2 * lane) = make_float2(acc[g][2] * corr, acc[g][3] * corr);
+    if (lane == 0) {
+      part_ml[((size_t)t * Hq + h) * 2] = mg * 1.4426950408889634f;
+      part_ml[((size_t)t * Hq + h) * 2 + 1] = lg;
+    }
+  }
+}
 }  // namespace
 
 // keep_first and the pooled cache (pk_cache null: none) as described at the top of this file
@@ -266,6 +388,24 @@ LLM_EXPORT int llm_attention_extras(const void* q, float* part_o, float* part_ml
   const bool vec = (page_stride % 8) == 0 && (((uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0 &&
                    (pk_cache == nullptr ||
                     ((p_page_stride % 8) == 0 && (((uintptr_t)pk_cache | (uintptr_t)pv_cache) & 15) == 0));
+  const int group = Hq / Hkv;
+  if (vec && (hd == 64 || hd == 128) && ((uintptr_t)q & 15) == 0 && ((uintptr_t)part_o & 7) == 0) {
+    const long long pairs = (long long)rows * Hkv;
+    const int nb = (int)((pairs + WARPS - 1) / WARPS);
+#define OUTSIDE_GO(G)                                                                                          \
+  attention_outside_kernel<G><<<nb, WARPS * 32, 0, stream>>>(                                                  \
+      (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, block_table, table_stride,      \
+      row_slot, row_pos, rows, Hq, Hkv, hd, page_size, scale, window, sink, keep_first, pooled, part_o, part_ml)
+    switch (group) {
+      case 1: OUTSIDE_GO(1); return launch_status();
+      case 2: OUTSIDE_GO(2); return launch_status();
+      case 4: OUTSIDE_GO(4); return launch_status();
+      case 8: OUTSIDE_GO(8); return launch_status();
+      case 16: OUTSIDE_GO(16); return launch_status();
+      default: break;
+    }
+#undef OUTSIDE_GO
+  }
   const long long items = (long long)rows * Hq;
   const int blocks = (int)((items + WARPS - 1) / WARPS);
 #define EXTRAS_GO(V)                                                                                          \

@@ -32,7 +32,16 @@ struct StoreArgs {
   float eps;
 };
 
-template <typename T>
+__device__ __forceinline__ void store2(float* dst, float a, float b) { *reinterpret_cast<float2*>(dst) = make_float2(a, b); }
+__device__ __forceinline__ void store2(bf16* dst, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(a, b);
+}
+
+// One block per (row, share of the heads); a warp per head in turn.  With a norm over whole rows
+// every block of a row sums the squares of the whole row itself.  PAIRS: all sizes are even and
+// the rows 8-byte aligned, so a lane reads and writes two adjacent channels at once, which are
+// also the two members of a rotated pair.
+template <typename T, bool PAIRS>
 __global__ void __launch_bounds__(256) qkv_store_kernel(const StoreArgs a) {
   __shared__ float scratch[33];
   pdl_trigger();
@@ -43,7 +52,14 @@ __global__ void __launch_bounds__(256) qkv_store_kernel(const StoreArgs a) {
   float whole_q = 1.f, whole_k = 1.f;
   if (a.norm == 2) {
     float s = 0.f;
-    for (int i = threadIdx.x; i < a.Hq * a.d; i += blockDim.x) s = fmaf(qr[i], qr[i], s);
+    if (PAIRS) {
+      for (int i = threadIdx.x; i < a.Hq * a.d / 2; i += blockDim.x) {
+        const float2 x = *reinterpret_cast<const float2*>(qr + 2 * i);
+        s = fmaf(x.x, x.x, s), s = fmaf(x.y, x.y, s);
+      }
+    } else {
+      for (int i = threadIdx.x; i < a.Hq * a.d; i += blockDim.x) s = fmaf(qr[i], qr[i], s);
+    }
     whole_q = rsqrtf(block_sum(s, scratch) / (float)(a.Hq * a.d) + a.eps);
     if (a.has_kv) {
       s = 0.f;
@@ -59,12 +75,20 @@ __global__ void __launch_bounds__(256) qkv_store_kernel(const StoreArgs a) {
   }
   const float* cs = a.cos_sin ? a.cos_sin + (size_t)r * (a.rot / 2) * 2 : nullptr;
   const int heads = a.Hq + (a.has_kv ? 2 * a.Hkv : 0);
-  for (int item = warp; item < heads; item += nwarps) {
+  for (int item = blockIdx.y * nwarps + warp; item < heads; item += nwarps * gridDim.y) {
     if (item >= a.Hq + a.Hkv) {                    // a value head: a copy, padded with zeros
       const int g = item - a.Hq - a.Hkv;
       const float* src = a.v + (size_t)r * a.v_stride + (size_t)g * a.dv;
       T* dst = (T*)a.v_cache + page_off + ((long long)g * a.page_size + pos % a.page_size) * a.hd;
-      for (int c = lane; c < a.hd; c += 32) dst[c] = from_f32<T>(c < a.dv ? src[c] : 0.f);
+      if (PAIRS) {
+        for (int c = 2 * lane; c < a.hd; c += 64) {
+          float2 x = make_float2(0.f, 0.f);
+          if (c < a.dv) x = *reinterpret_cast<const float2*>(src + c);
+          store2(dst + c, x.x, x.y);
+        }
+      } else {
+        for (int c = lane; c < a.hd; c += 32) dst[c] = from_f32<T>(c < a.dv ? src[c] : 0.f);
+      }
       continue;
     }
     const bool is_q = item < a.Hq;
@@ -78,15 +102,34 @@ __global__ void __launch_bounds__(256) qkv_store_kernel(const StoreArgs a) {
       scale = rsqrtf(warp_sum(s) / (float)a.d + a.eps);
     }
     if (w && a.norm == 2) w += (size_t)h * a.d;
+    if (!a.norm) w = nullptr;
     T* dst = is_q ? (T*)a.q_out + ((size_t)r * a.Hq + h) * a.hd
                   : (T*)a.k_cache + page_off + ((long long)h * a.page_size + pos % a.page_size) * a.hd;
+    if (PAIRS) {
+      for (int c = 2 * lane; c < a.hd; c += 64) {
+        float x = 0.f, y = 0.f;
+        if (c < a.d) {
+          const float2 u = *reinterpret_cast<const float2*>(src + c);
+          x = u.x * scale * (w ? w[c] : 1.f);
+          y = u.y * scale * (w ? w[c + 1] : 1.f);
+          if (cs && c < a.rot) {
+            const float2 t = *reinterpret_cast<const float2*>(cs + c);      // (cos, sin) of pair c / 2
+            const float x2 = fmaf(x, t.x, -(y * t.y));
+            y = fmaf(y, t.x, x * t.y);
+            x = x2;
+          }
+        }
+        store2(dst + c, x, y);
+      }
+      continue;
+    }
     for (int c = lane; c < a.hd; c += 32) {
       float x = 0.f;
       if (c < a.d) {
-        x = src[c] * scale * (w && a.norm ? w[c] : 1.f);
+        x = src[c] * scale * (w ? w[c] : 1.f);
         if (cs && c < a.rot) {
           const int o = c ^ 1;                       // the other member of the pair
-          const float y = src[o] * scale * (w && a.norm ? w[o] : 1.f);
+          const float y = src[o] * scale * (w ? w[o] : 1.f);
           const float co = cs[(c >> 1) * 2], si = cs[(c >> 1) * 2 + 1];
           x = (c & 1) ? fmaf(x, co, y * si) : fmaf(x, co, -(y * si));
         }
@@ -96,12 +139,17 @@ __global__ void __launch_bounds__(256) qkv_store_kernel(const StoreArgs a) {
   }
 }
 
+// A block per (row that ends a block of P positions, key head): `subs` groups of hd threads share
+// out the block's positions (group s takes s, s + subs, ...), a thread per channel sums its
+// group's keys and values, and the groups' sums are added in order through shared memory.  Which
+// positions a sum visits in which order depends on P, hd and subs only.
 template <typename T>
-__global__ void __launch_bounds__(128) pool_blocks_kernel(
+__global__ void __launch_bounds__(1024) pool_blocks_kernel(
     const T* __restrict__ k_cache, const T* __restrict__ v_cache, long long page_stride,
     const int* __restrict__ table, int table_stride, T* __restrict__ pk_cache, T* __restrict__ pv_cache,
     long long p_page_stride, const int* __restrict__ p_table, int p_table_stride, const int* __restrict__ row_slot,
-    const int* __restrict__ row_pos, int Hkv, int hd, int page_size, int P) {
+    const int* __restrict__ row_pos, int Hkv, int hd, int page_size, int P, int subs) {
+  extern __shared__ float sums[];      // [subs][2][hd]
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.x, g = blockIdx.y;
@@ -109,20 +157,30 @@ __global__ void __launch_bounds__(128) pool_blocks_kernel(
   if (pos % P != P - 1) return;
   const int b = pos / P, slot = row_slot[r];
   const int* tab = table + (size_t)slot * table_stride;
+  const int sub = threadIdx.x / hd, c = threadIdx.x % hd;
+  if (sub < subs) {
+    float sk = 0.f, sv = 0.f;
+    int p = b * P + sub;
+    int page = p / page_size, in = p % page_size;
+#pragma unroll 4
+    for (int j = sub; j < P; j += subs) {
+      const long long off = (long long)tab[page] * page_stride + ((long long)g * page_size + in) * hd + c;
+      sk += to_f32(k_cache[off]);
+      sv += to_f32(v_cache[off]);
+      in += subs;
+      while (in >= page_size) in -= page_size, ++page;
+    }
+    sums[(sub * 2) * hd + c] = sk, sums[(sub * 2 + 1) * hd + c] = sv;
+  }
+  __syncthreads();
+  if (sub != 0) return;
+  float sk = 0.f, sv = 0.f;
+  for (int s = 0; s < subs; ++s) sk += sums[(s * 2) * hd + c], sv += sums[(s * 2 + 1) * hd + c];
   const int dst_page = p_table[(size_t)slot * p_table_stride + b / page_size];
   const long long dst = (long long)dst_page * p_page_stride + ((long long)g * page_size + b % page_size) * hd;
   const float inv = 1.0f / (float)P;
-  for (int c = threadIdx.x; c < hd; c += blockDim.x) {
-    float sk = 0.f, sv = 0.f;
-    for (int j = 0; j < P; ++j) {
-      const int p = b * P + j;
-      const long long off = (long long)tab[p / page_size] * page_stride + ((long long)g * page_size + p % page_size) * hd + c;
-      sk += to_f32(k_cache[off]);
-      sv += to_f32(v_cache[off]);
-    }
-    pk_cache[dst + c] = from_f32<T>(sk * inv);
-    pv_cache[dst + c] = from_f32<T>(sv * inv);
-  }
+  pk_cache[dst + c] = from_f32<T>(sk * inv);
+  pv_cache[dst + c] = from_f32<T>(sv * inv);
 }
 }  // namespace
 
@@ -145,11 +203,26 @@ LLM_EXPORT int llm_qkv_store(const float* q, int q_stride, const float* k, int k
   a.dv = dv, a.hd = hd, a.rot = rot, a.norm = norm, a.has_kv = has_kv, a.eps = eps;
   const int heads = Hq + (has_kv ? 2 * Hkv : 0);
   const int threads = heads >= 8 ? 256 : heads >= 4 ? 128 : 64;
+  // few rows: the heads of a row are shared out to several blocks, so that the step fills the GPU
+  int shares = 1;
+  if (rows < 1024) {
+    shares = (heads + threads / 32 - 1) / (threads / 32);
+    if (shares > 8) shares = 8;
+  }
+  const bool even = !((d | dv | hd | q_stride) & 1) && !((uintptr_t)q & 7) && !((uintptr_t)q_out & 7) &&
+                    (!has_kv || (!((k_stride | v_stride) & 1) && !(page_stride & 1) &&
+                                 !(((uintptr_t)k | (uintptr_t)v | (uintptr_t)k_cache | (uintptr_t)v_cache) & 7))) &&
+                    (rot == 0 || !((uintptr_t)cos_sin & 7));
+  const dim3 grid(rows, shares);
   int rc;
-  if (dtype == LLM_F32) rc = launch_pdl(qkv_store_kernel<float>, rows, threads, 0, stream, a);
-  else if (dtype == LLM_BF16) rc = launch_pdl(qkv_store_kernel<bf16>, rows, threads, 0, stream, a);
+#define STORE_GO(T) \
+  rc = even ? launch_pdl(qkv_store_kernel<T, true>, grid, threads, 0, stream, a) \
+            : launch_pdl(qkv_store_kernel<T, false>, grid, threads, 0, stream, a)
+  if (dtype == LLM_F32) STORE_GO(float);
+  else if (dtype == LLM_BF16) STORE_GO(bf16);
   else return LLM_ERR_UNSUPPORTED;
-  return launched_many_blocks(rc, rows);
+#undef STORE_GO
+  return launched_many_blocks(rc, (long long)rows * shares);
 }
 
 LLM_EXPORT int llm_pool_blocks(const void* k_cache, const void* v_cache, long long page_stride, const int* table,
@@ -158,17 +231,21 @@ LLM_EXPORT int llm_pool_blocks(const void* k_cache, const void* v_cache, long lo
                                int dtype, int rows, int Hkv, int hd, int page_size, int P, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (P <= 0 || Hkv <= 0 || Hkv > 65535) return LLM_ERR_ARGUMENT;
+  if (hd <= 0 || hd > 1024) return LLM_ERR_UNSUPPORTED;
   const dim3 grid(rows, Hkv);
-  const int threads = hd >= 128 ? 128 : 64;
+  int subs = hd >= 256 ? 1 : 256 / hd;
+  if (subs > P) subs = P;
+  const int threads = (subs * hd + 31) / 32 * 32;
+  const int smem = subs * 2 * hd * (int)sizeof(float);
   int rc;
   if (dtype == LLM_F32)
-    rc = launch_pdl(pool_blocks_kernel<float>, grid, threads, 0, stream, (const float*)k_cache, (const float*)v_cache,
-                    page_stride, table, table_stride, (float*)pk_cache, (float*)pv_cache, p_page_stride, p_table,
-                    p_table_stride, row_slot, row_pos, Hkv, hd, page_size, P);
+    rc = launch_pdl(pool_blocks_kernel<float>, grid, threads, smem, stream, (const float*)k_cache,
+                    (const float*)v_cache, page_stride, table, table_stride, (float*)pk_cache, (float*)pv_cache,
+                    p_page_stride, p_table, p_table_stride, row_slot, row_pos, Hkv, hd, page_size, P, subs);
   else if (dtype == LLM_BF16)
-    rc = launch_pdl(pool_blocks_kernel<bf16>, grid, threads, 0, stream, (const bf16*)k_cache, (const bf16*)v_cache,
-                    page_stride, table, table_stride, (bf16*)pk_cache, (bf16*)pv_cache, p_page_stride, p_table,
-                    p_table_stride, row_slot, row_pos, Hkv, hd, page_size, P);
+    rc = launch_pdl(pool_blocks_kernel<bf16>, grid, threads, smem, stream, (const bf16*)k_cache,
+                    (const bf16*)v_cache, page_stride, table, table_stride, (bf16*)pk_cache, (bf16*)pv_cache,
+                    p_page_stride, p_table, p_table_stride, row_slot, row_pos, Hkv, hd, page_size, P, subs);
   else return LLM_ERR_UNSUPPORTED;
   return launched_many_blocks(rc, (long long)rows * Hkv);
 }

@@ -732,9 +732,8 @@ LLM_EXPORT int llm_causal_conv_silu(const float* src, int src_stride, const floa
 //   S <- (1 - z) S + z c;  out = S * silu(g)                              (all 32-bit)
 // Two passes.  The first is elementwise over the step: it overwrites zr with the weight 1 - z
 // of the old state, ur with z c and g with silu(g).  The second walks every request's rows in
-// order, a thread per (request, channel), with one multiply-add per token in the chain; the
-// state is carried through memory unrounded, so a row's result does not depend on how the
-// tokens were cut into steps.
+// order with one multiply-add per token in the chain; the state is carried through memory
+// unrounded.  Steps of single tokens take a thread per (request, channel).
 __global__ void min_gru_gates_kernel(float* __restrict__ z, float* __restrict__ u, float* __restrict__ g,
                                      int stride, const float* __restrict__ bz, const float* __restrict__ bx,
                                      long long total, int width) {
@@ -783,6 +782,55 @@ __global__ void __launch_bounds__(128) min_gru_scan_kernel(const float* __restri
   *sp = S;
 }
 
+// The same walk for steps that hold portions of prompts: a block per (request, 32 channels) cuts
+// the request's rows into as many runs as it has warps.  S <- k S + a is a chain of affine maps, so
+// every warp first folds its run into one map (the product of the k and the run's result from
+// zero), the maps of the runs before a warp give the state that enters its run, and a second walk
+// writes the rows.  The chain a row waits for is 2 / warps of the portion; the sums are 32-bit and
+// differ from the token-by-token walk by rounding only.
+constexpr int GRU_WARPS = 16;
+
+template <typename TOut>
+__global__ void __launch_bounds__(GRU_WARPS * 32) min_gru_runs_kernel(
+    const float* __restrict__ keep, const float* __restrict__ add, const float* __restrict__ gate, int stride,
+    float* __restrict__ state, long long state_stride, TOut* __restrict__ out, int out_stride,
+    const int* __restrict__ seg, int width) {
+  __shared__ float map_k[GRU_WARPS][32], map_a[GRU_WARPS][32];
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int c = blockIdx.y * 32 + lane, slot = blockIdx.x;
+  const int first = seg[SEG * slot], end = seg[SEG * slot + 1];
+  if (end <= first) return;
+  const bool live = c < width;
+  const int n = end - first, per = (n + GRU_WARPS - 1) / GRU_WARPS;
+  const int r0 = first + (w * per < n ? w * per : n), r1 = first + ((w + 1) * per < n ? (w + 1) * per : n);
+  float K = 1.f, A = 0.f;
+  if (live) {
+#pragma unroll 4
+    for (int r = r0; r < r1; ++r) {
+      const size_t at = (size_t)r * stride + c;
+      const float k = keep[at];
+      K *= k;
+      A = fmaf(k, A, add[at]);
+    }
+  }
+  map_k[w][lane] = K, map_a[w][lane] = A;
+  // (the old state is read on this side of the barrier, the new one written on the other)
+  float* sp = state + (size_t)slot * state_stride + (live ? c : 0);
+  float S = *sp;
+  __syncthreads();
+  if (!live) return;
+  for (int j = 0; j < w; ++j) S = fmaf(map_k[j][lane], S, map_a[j][lane]);
+#pragma unroll 4
+  for (int r = r0; r < r1; ++r) {
+    const size_t at = (size_t)r * stride + c;
+    S = fmaf(keep[at], S, add[at]);
+    out[(size_t)r * out_stride + c] = from_f32<TOut>(S * gate[at]);
+  }
+  if (w == GRU_WARPS - 1) *sp = S;
+}
+
 // z, u, g: three column ranges of one float32 matrix of row stride `stride` (overwritten);
 // state float32 [slots][>= width]; out [rows][width] in out_dtype.
 LLM_EXPORT int llm_min_gru(float* z, float* u, float* g, int stride, const float* bz, const float* bx,
@@ -795,7 +843,19 @@ LLM_EXPORT int llm_min_gru(float* z, float* u, float* g, int stride, const float
   const int blocks = (int)((total + 255) / 256 < 2368 ? (total + 255) / 256 : 2368);
   int rc = launch_pdl(min_gru_gates_kernel, blocks, 256, 0, stream, z, u, g, stride, bz, bx, total, width);
   if (rc) return rc;
-  const dim3 grid(single ? rows : n_slots, (width + 127) / 128);
+  if (!single) {
+    const dim3 grid(n_slots, (width + 31) / 32);
+    if (out_dtype == LLM_F32)
+      return launch_pdl(min_gru_runs_kernel<float>, grid, GRU_WARPS * 32, 0, stream, (const float*)z,
+                        (const float*)u, (const float*)g, stride, state, state_stride, (float*)out, out_stride,
+                        seg, width);
+    if (out_dtype == LLM_BF16)
+      return launch_pdl(min_gru_runs_kernel<bf16>, grid, GRU_WARPS * 32, 0, stream, (const float*)z,
+                        (const float*)u, (const float*)g, stride, state, state_stride, (bf16*)out, out_stride, seg,
+                        width);
+    return LLM_ERR_UNSUPPORTED;
+  }
+  const dim3 grid(rows, (width + 127) / 128);
   if (out_dtype == LLM_F32)
     return launch_pdl(min_gru_scan_kernel<float>, grid, 128, 0, stream, (const float*)z, (const float*)u,
                       (const float*)g, stride, state, state_stride, (float*)out, out_stride, row_slot, seg, single,

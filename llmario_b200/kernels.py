@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -70,6 +70,11 @@ def _signatures():
         "llm_attention_merge_clear": [P, P, P, P, I, I, I, I, P, I, P],
         "llm_attention_merge_sink": [P, P, P, P, I, I, I, I, P, I, P, P],
         "llm_attention_tcgen05_sink": [P, P, I, P, P, L, L, P, I, P, I, I, I, I, I, F, I, I, P, P, P],
+        "llm_attention_tcgen05_extra": [P, P, I, P, P, L, L, P, I, P, I, I, I, I, I, F, I, I, P, P, P,
+                                        P, P],
+        "llm_attention_merge_extra": [P, P, P, P, I, I, I, I, P, I, P, P, P, P],
+        "llm_attention_extras": [P, P, P, P, P, L, P, I, P, P, I, I, I, I, I, F, I, P, I, P, P, L, P,
+                                 I, I, P],
         "llm_attention_decode_fused": [P, I, P, P, P, P, L, I, I, P, P, L, P, I, P, P, I, P, P, P,
                                        F, I, I, I, I, I, F, I, I, P, P],
         "llm_attention_decode": [P, P, P, P, P, P, L, P, I, P, P, P, I, I, I, I, I, F, I, I, P],
@@ -927,20 +932,56 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                       v_cache: torch.Tensor, page_stride: int, block_table: torch.Tensor,
                       items: torch.Tensor, n_items: int, num_heads: int, num_kv_heads: int,
                       head_dim: int, page_size: int, scale: float, window: Optional[int],
-                      n_pages: int = 0, persistent: bool = True) -> None:
+                      n_pages: int = 0, persistent: bool = True,
+                      sink: Optional[torch.Tensor] = None,
+                      outside: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> None:
     """Attention of prompt portions on tcgen05: items of at most 128 / (heads per KV head)
     tokens; scores and output accumulate in tensor memory.  ``n_pages``: pages of the cache that
     ``k_cache`` / ``v_cache`` are planes of; given it, pages of 32 positions or more are
     fetched by TMA, and with ``persistent`` and more (item, KV head) pairs than SMs one CTA per
-    SM walks its share of the pairs."""
-    _cuda(q, out, k_cache, v_cache, block_table, items)
+    SM walks its share of the pairs.  ``sink`` (float32 [heads]) joins every row's sum as
+    ``exp(sink)``; ``outside``: the two buffers of :func:`attention_outside`, one more part of
+    every row's softmax."""
+    eo, eml = outside if outside is not None else (None, None)
+    _cuda(q, out, k_cache, v_cache, block_table, items, sink, eo, eml)
     assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
     assert q.is_contiguous() and out.is_contiguous()
-    _check(lib().llm_attention_tcgen05(
+    _check(lib().llm_attention_tcgen05_extra(
         _ptr(q), _ptr(out), q.shape[0], _ptr(k_cache), _ptr(v_cache), page_stride, int(n_pages),
         _ptr(block_table), block_table.stride(0), _ptr(items), n_items, num_heads, num_kv_heads,
         head_dim, page_size, float(scale), int(window or 0), int(persistent),
-        _ptr(tc_status(q.device)), _stream()), f"attention_tcgen05 (head_dim {head_dim})")
+        _ptr(tc_status(q.device)), _ptr(sink), _ptr(eo), _ptr(eml), _stream()),
+        f"attention_tcgen05 (head_dim {head_dim})")
+
+
+def attention_outside(q: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor, view,
+                      row_slot: torch.Tensor, row_pos: torch.Tensor, num_heads: int,
+                      num_kv_heads: int, head_dim: int, scale: float, window: int,
+                      sink: Optional[torch.Tensor] = None, keep_first: int = 0, pool: int = 0,
+                      pooled_view=None) -> None:
+    """What every row of a step sees outside its window of the last ``window`` keys, as one part
+    of its softmax per head: the first ``keep_first`` keys of its sequence that the window has
+    passed, the entries of ``pooled_view`` (one per block of ``pool`` positions) whose blocks
+    lie wholly behind the window, and ``exp(sink)``.  part_o float32 [rows, heads, head_dim]
+    (weighted values, not divided), part_ml float32 [rows, heads, 2] (the maximum as a base-2
+    logarithm, the sum of weights): :func:`attention_tcgen05` and :func:`attention_merge` take
+    them in.  bfloat16."""
+    pk = pv = pt = None
+    pstride = ptstride = 0
+    if pool:
+        pk, pv, pt = pooled_view.k, pooled_view.v, pooled_view.block_table
+        pstride, ptstride = pooled_view.page_stride, pt.stride(0)
+    _cuda(q, part_o, part_ml, view.k, view.v, view.block_table, row_slot, row_pos, sink, pk, pv, pt)
+    assert q.dtype == torch.bfloat16 and view.k.dtype == torch.bfloat16 and q.is_contiguous()
+    assert part_o.dtype == part_ml.dtype == torch.float32
+    rows = q.shape[0]
+    assert part_o.numel() >= rows * num_heads * head_dim and part_ml.numel() >= rows * num_heads * 2
+    _check(lib().llm_attention_extras(
+        _ptr(q), _ptr(part_o), _ptr(part_ml), _ptr(view.k), _ptr(view.v), view.page_stride,
+        _ptr(view.block_table), view.block_table.stride(0), _ptr(row_slot), _ptr(row_pos), rows,
+        num_heads, num_kv_heads, head_dim, view.page_size, float(scale), int(window), _ptr(sink),
+        int(keep_first), _ptr(pk), _ptr(pv), pstride, _ptr(pt), ptstride, int(pool), _stream()),
+        f"attention_outside (head_dim {head_dim})")
 
 
 def attention_tcgen05_x2(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
@@ -969,13 +1010,18 @@ def decode_tma_ok(view, head_dim: int) -> bool:
 
 def attention_merge(part_o: torch.Tensor, part_ml: torch.Tensor, out: torch.Tensor,
                     rows: Optional[torch.Tensor], n_rows: int, num_heads: int, head_dim: int,
-                    splits: int, clear: Optional[torch.Tensor] = None) -> None:
+                    splits: int, clear: Optional[torch.Tensor] = None,
+                    sink: Optional[torch.Tensor] = None,
+                    outside: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> None:
     """Merge the parts of split keys.  ``clear`` (float32 [rows, >= heads * head_dim]): the
-    first heads * head_dim values of every merged row of it are zeroed as well."""
-    _cuda(part_o, part_ml, out, rows, clear)
-    _check(lib().llm_attention_merge_clear(
+    first heads * head_dim values of every merged row of it are zeroed as well.  ``sink`` and
+    ``outside`` as in :func:`attention_tcgen05`."""
+    eo, eml = outside if outside is not None else (None, None)
+    _cuda(part_o, part_ml, out, rows, clear, sink, eo, eml)
+    _check(lib().llm_attention_merge_extra(
         _ptr(part_o), _ptr(part_ml), _ptr(out), _ptr(rows), n_rows, num_heads, head_dim, splits,
-        _ptr(clear), clear.stride(0) if clear is not None else 0, _stream()), "attention_merge")
+        _ptr(clear), clear.stride(0) if clear is not None else 0, _ptr(sink), _ptr(eo), _ptr(eml),
+        _stream()), "attention_merge")
 
 
 FUSE_DECODE = "few waves"     # or "always" / "never": for measurements (see fuse_decode)

@@ -86,6 +86,12 @@ CONFIGS: Dict[str, dict] = {
                             rot=6, mlp=moe(experts=3, top=2, identity=1, ff=9)),
                    attention(heads=2, kv_heads=2, dim=10, vdim=14, size=5, keep=2,
                              mlp=dense(34))], width=50, vocab=33),
+    # heads of 128 channels, sixteen and four query heads on a key head: the sizes at which the
+    # keys outside the window have a kernel for a whole group of heads
+    "wide_heads": config([parallel(width=32, heads=16, kv_heads=1, dim=128, vdim=128, conv=2, size=19,
+                                   pool=4, rot=64),
+                          attention(heads=8, kv_heads=2, dim=128, vdim=128, size=13, keep=6,
+                                    mlp=dense(48))], width=64, vocab=80),
     # all of them, in an order of their own
     "mix": config([attention(size=21, keep=4, mlp=moe()),
                    parallel(mlp=moe(experts=4, top=2, identity=1)),

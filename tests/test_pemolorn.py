@@ -363,7 +363,8 @@ def test_portions_of_many_sizes(name, dtype):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ("mix", "shared", "odd", "par_big_pool", "par_pool1", "attn_keep"))
+@pytest.mark.parametrize("name", ("mix", "shared", "odd", "par_big_pool", "par_pool1", "attn_keep",
+                                  "wide_heads"))
 def test_mixed_batches_and_reused_slots(name, dtype):
     """Four request slots, six requests of unequal lengths: portions of some beside single tokens
     of others, requests that pause, requests that end and whose slot and pages the next one
