@@ -203,9 +203,10 @@ __global__ void __launch_bounds__(WARPS * 32) attention_outside_kernel(
     float* __restrict__ part_ml) {
   __shared__ __align__(16) float q_s[WARPS][GROUP][128];
   const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * WARPS + warp_in_block;
-  if (item >= (long long)rows * Hkv) return;
-  const int t = (int)(item / Hkv), kvh = (int)(item % Hkv);
+  // (the warps of a block are adjacent rows on one key head: in a prompt's portion they read the
+  // same entries at about the same time, which the first-level cache then serves)
+  const int t = blockIdx.x * WARPS + warp_in_block, kvh = blockIdx.y;
+  if (t >= rows) return;
   const int pos = row_pos[t], slot = row_slot[t];
   const int* table = block_table + (size_t)slot * table_stride;
   const int behind = pos - window + 1 > 0 ? pos - window + 1 : 0;      // positions the window has passed
@@ -246,6 +247,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_outside_kernel(
 #pragma unroll
     for (int g = 0; g < GROUP; ++g) w[g] = 0.f;
     if (valid) {
+#pragma unroll 4
       for (int i = 0; i < hd; i += 8) {
         Vec8<bf16> kv;
         kv.load(kr + i);
@@ -271,23 +273,32 @@ __global__ void __launch_bounds__(WARPS * 32) attention_outside_kernel(
       acc[g][0] *= corr, acc[g][1] *= corr, acc[g][2] *= corr, acc[g][3] *= corr;
       m[g] = m_new;
     }
-    for (int j = 0; j < 32; ++j) {
-      if (!((mask >> j) & 1u)) break;      // the entries of a tile are its first lanes
-      const bf16* vj = (const bf16*)__shfl_sync(0xffffffffu, (unsigned long long)vr, j);
-      float2 v0 = make_float2(0.f, 0.f), v1 = v0;
-      {
-        const uint32_t u = *reinterpret_cast<const uint32_t*>(vj + 2 * lane);
-        v0 = make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
-      }
-      if (pairs > 1) {
-        const uint32_t u = *reinterpret_cast<const uint32_t*>(vj + 64 + 2 * lane);
-        v1 = make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+    const int nv = __popc(mask);      // the entries of a tile are its first lanes
+    for (int j0 = 0; j0 < nv; j0 += 4) {
+      // four value rows at a time: their loads are under way together
+      float2 v0[4], v1[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const bf16* vj = (const bf16*)__shfl_sync(0xffffffffu, (unsigned long long)vr, (j0 + i) & 31);
+        v0[i] = v1[i] = make_float2(0.f, 0.f);
+        if (j0 + i < nv) {
+          const uint32_t a = *reinterpret_cast<const uint32_t*>(vj + 2 * lane);
+          v0[i] = make_float2(__uint_as_float(a << 16), __uint_as_float(a & 0xffff0000u));
+          if (pairs > 1) {
+            const uint32_t b = *reinterpret_cast<const uint32_t*>(vj + 64 + 2 * lane);
+            v1[i] = make_float2(__uint_as_float(b << 16), __uint_as_float(b & 0xffff0000u));
+          }
+        }
       }
 #pragma unroll
-      for (int g = 0; g < GROUP; ++g) {
-        const float wj = __shfl_sync(0xffffffffu, w[g], j);
-        acc[g][0] = fmaf(wj, v0.x, acc[g][0]), acc[g][1] = fmaf(wj, v0.y, acc[g][1]);
-        acc[g][2] = fmaf(wj, v1.x, acc[g][2]), acc[g][3] = fmaf(wj, v1.y, acc[g][3]);
+      for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int g = 0; g < GROUP; ++g) {
+          // (a lane behind the tile's entries has the weight 0 and met zeros above)
+          const float wj = __shfl_sync(0xffffffffu, w[g], (j0 + i) & 31);
+          acc[g][0] = fmaf(wj, v0[i].x, acc[g][0]), acc[g][1] = fmaf(wj, v0[i].y, acc[g][1]);
+          acc[g][2] = fmaf(wj, v1[i].x, acc[g][2]), acc[g][3] = fmaf(wj, v1[i].y, acc[g][3]);
+        }
       }
     }
   }
@@ -390,8 +401,8 @@ LLM_EXPORT int llm_attention_extras(const void* q, float* part_o, float* part_ml
                     ((p_page_stride % 8) == 0 && (((uintptr_t)pk_cache | (uintptr_t)pv_cache) & 15) == 0));
   const int group = Hq / Hkv;
   if (vec && (hd == 64 || hd == 128) && ((uintptr_t)q & 15) == 0 && ((uintptr_t)part_o & 7) == 0) {
-    const long long pairs = (long long)rows * Hkv;
-    const int nb = (int)((pairs + WARPS - 1) / WARPS);
+    if (Hkv > 65535) return LLM_ERR_UNSUPPORTED;
+    const dim3 nb((rows + WARPS - 1) / WARPS, Hkv);
 #define OUTSIDE_GO(G)                                                                                          \
   attention_outside_kernel<G><<<nb, WARPS * 32, 0, stream>>>(                                                  \
       (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, block_table, table_stride,      \

@@ -730,56 +730,32 @@ LLM_EXPORT int llm_causal_conv_silu(const float* src, int src_stride, const floa
 // ---- minGRU: a gated recurrence per channel whose gates read only the current token
 //   z = sigmoid(zr + bz), u = ur + bx, candidate c = u + 1/2 (u >= 0) or sigmoid(u) (u < 0)
 //   S <- (1 - z) S + z c;  out = S * silu(g)                              (all 32-bit)
-// Two passes.  The first is elementwise over the step: it overwrites zr with the weight 1 - z
-// of the old state, ur with z c and g with silu(g).  The second walks every request's rows in
-// order with one multiply-add per token in the chain; the state is carried through memory
-// unrounded.  Steps of single tokens take a thread per (request, channel).
-__global__ void min_gru_gates_kernel(float* __restrict__ z, float* __restrict__ u, float* __restrict__ g,
-                                     int stride, const float* __restrict__ bz, const float* __restrict__ bx,
-                                     long long total, int width) {
-  pdl_trigger();
-  pdl_wait();
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const long long r = i / width;
-    const int c = (int)(i - r * width);
-    const size_t at = (size_t)r * stride + c;
-    const float zz = 1.f / (1.f + expf(-(z[at] + (bz ? bz[c] : 0.f))));
-    const float uu = u[at] + (bx ? bx[c] : 0.f);
-    const float cand = uu >= 0.f ? uu + 0.5f : 1.f / (1.f + expf(-uu));
-    z[at] = 1.f - zz;
-    u[at] = zz * cand;
-    g[at] = silu_f(g[at]);
-  }
+// The state is carried through memory unrounded.  A step of single tokens takes a thread per
+// (row, channel): the gates, one multiply-add, the output.
+__device__ __forceinline__ void min_gru_gate(float zr, float ur, float bz, float bx, float& keep, float& add) {
+  const float zz = 1.f / (1.f + expf(-(zr + bz)));
+  const float uu = ur + bx;
+  const float cand = uu >= 0.f ? uu + 0.5f : 1.f / (1.f + expf(-uu));
+  keep = 1.f - zz;
+  add = zz * cand;
 }
 
 template <typename TOut>
-__global__ void __launch_bounds__(128) min_gru_scan_kernel(const float* __restrict__ keep, const float* __restrict__ add,
-                                                           const float* __restrict__ gate, int stride,
-                                                           float* __restrict__ state, long long state_stride,
-                                                           TOut* __restrict__ out, int out_stride,
-                                                           const int* __restrict__ row_slot,
-                                                           const int* __restrict__ seg, int single, int width) {
+__global__ void __launch_bounds__(128) min_gru_token_kernel(
+    const float* __restrict__ z, const float* __restrict__ u, const float* __restrict__ g, int stride,
+    const float* __restrict__ bz, const float* __restrict__ bx, float* __restrict__ state, long long state_stride,
+    TOut* __restrict__ out, int out_stride, const int* __restrict__ row_slot, int width) {
   pdl_trigger();
   pdl_wait();
-  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x, r = blockIdx.x;
   if (c >= width) return;
-  int slot, first, end;
-  if (single) {
-    first = blockIdx.x, end = first + 1, slot = row_slot[first];
-  } else {
-    slot = blockIdx.x;
-    first = seg[SEG * slot], end = seg[SEG * slot + 1];
-  }
-  if (end <= first) return;
-  float* sp = state + (size_t)slot * state_stride + c;
-  float S = *sp;
-  for (int r = first; r < end; ++r) {
-    const size_t at = (size_t)r * stride + c;
-    S = fmaf(keep[at], S, add[at]);
-    out[(size_t)r * out_stride + c] = from_f32<TOut>(S * gate[at]);
-  }
+  const size_t at = (size_t)r * stride + c;
+  float k, a;
+  min_gru_gate(z[at], u[at], bz ? bz[c] : 0.f, bx ? bx[c] : 0.f, k, a);
+  float* sp = state + (size_t)row_slot[r] * state_stride + c;
+  const float S = fmaf(k, *sp, a);
   *sp = S;
+  out[(size_t)r * out_stride + c] = from_f32<TOut>(S * silu_f(g[at]));
 }
 
 // The same walk for steps that hold portions of prompts: a block per (request, 32 channels) cuts
@@ -787,14 +763,18 @@ __global__ void __launch_bounds__(128) min_gru_scan_kernel(const float* __restri
 // every warp first folds its run into one map (the product of the k and the run's result from
 // zero), the maps of the runs before a warp give the state that enters its run, and a second walk
 // writes the rows.  The chain a row waits for is 2 / warps of the portion; the sums are 32-bit and
-// differ from the token-by-token walk by rounding only.
-constexpr int GRU_WARPS = 16;
+// differ from the token-by-token walk by rounding only.  Rows are taken eight at a time, so that
+// their loads and their gates (which do not wait for the chain) overlap.
+constexpr int GRU_WARPS = 32;
+constexpr int GRU_BATCH = 8;      // rows whose loads and gates are under way together
+
+// It makes the gates in both walks, with the expressions of the kernel above.
 
 template <typename TOut>
 __global__ void __launch_bounds__(GRU_WARPS * 32) min_gru_runs_kernel(
-    const float* __restrict__ keep, const float* __restrict__ add, const float* __restrict__ gate, int stride,
-    float* __restrict__ state, long long state_stride, TOut* __restrict__ out, int out_stride,
-    const int* __restrict__ seg, int width) {
+    const float* __restrict__ z, const float* __restrict__ u, const float* __restrict__ g, int stride,
+    const float* __restrict__ bz, const float* __restrict__ bx, float* __restrict__ state, long long state_stride,
+    TOut* __restrict__ out, int out_stride, const int* __restrict__ seg, int width) {
   __shared__ float map_k[GRU_WARPS][32], map_a[GRU_WARPS][32];
   pdl_trigger();
   pdl_wait();
@@ -805,14 +785,22 @@ __global__ void __launch_bounds__(GRU_WARPS * 32) min_gru_runs_kernel(
   const bool live = c < width;
   const int n = end - first, per = (n + GRU_WARPS - 1) / GRU_WARPS;
   const int r0 = first + (w * per < n ? w * per : n), r1 = first + ((w + 1) * per < n ? (w + 1) * per : n);
+  const float bzc = live && bz ? bz[c] : 0.f, bxc = live && bx ? bx[c] : 0.f;
   float K = 1.f, A = 0.f;
   if (live) {
-#pragma unroll 4
-    for (int r = r0; r < r1; ++r) {
-      const size_t at = (size_t)r * stride + c;
-      const float k = keep[at];
-      K *= k;
-      A = fmaf(k, A, add[at]);
+    for (int r = r0; r < r1; r += GRU_BATCH) {
+      float zr[GRU_BATCH], ur[GRU_BATCH];
+#pragma unroll
+      for (int i = 0; i < GRU_BATCH; ++i) {
+        const size_t at = (size_t)(r + i < r1 ? r + i : r1 - 1) * stride + c;
+        zr[i] = z[at], ur[i] = u[at];
+      }
+#pragma unroll
+      for (int i = 0; i < GRU_BATCH; ++i) {
+        float k, a;
+        min_gru_gate(zr[i], ur[i], bzc, bxc, k, a);
+        if (r + i < r1) K *= k, A = fmaf(k, A, a);
+      }
     }
   }
   map_k[w][lane] = K, map_a[w][lane] = A;
@@ -822,16 +810,28 @@ __global__ void __launch_bounds__(GRU_WARPS * 32) min_gru_runs_kernel(
   __syncthreads();
   if (!live) return;
   for (int j = 0; j < w; ++j) S = fmaf(map_k[j][lane], S, map_a[j][lane]);
-#pragma unroll 4
-  for (int r = r0; r < r1; ++r) {
-    const size_t at = (size_t)r * stride + c;
-    S = fmaf(keep[at], S, add[at]);
-    out[(size_t)r * out_stride + c] = from_f32<TOut>(S * gate[at]);
+  for (int r = r0; r < r1; r += GRU_BATCH) {
+    float zr[GRU_BATCH], ur[GRU_BATCH], gr[GRU_BATCH];
+#pragma unroll
+    for (int i = 0; i < GRU_BATCH; ++i) {
+      const size_t at = (size_t)(r + i < r1 ? r + i : r1 - 1) * stride + c;
+      zr[i] = z[at], ur[i] = u[at], gr[i] = g[at];
+    }
+#pragma unroll
+    for (int i = 0; i < GRU_BATCH; ++i) {
+      float k, a;
+      min_gru_gate(zr[i], ur[i], bzc, bxc, k, a);
+      const float gate = silu_f(gr[i]);
+      if (r + i < r1) {
+        S = fmaf(k, S, a);
+        out[(size_t)(r + i) * out_stride + c] = from_f32<TOut>(S * gate);
+      }
+    }
   }
   if (w == GRU_WARPS - 1) *sp = S;
 }
 
-// z, u, g: three column ranges of one float32 matrix of row stride `stride` (overwritten);
+// z, u, g: three column ranges of one float32 matrix of row stride `stride`;
 // state float32 [slots][>= width]; out [rows][width] in out_dtype.
 LLM_EXPORT int llm_min_gru(float* z, float* u, float* g, int stride, const float* bz, const float* bx,
                            float* state, long long state_stride, void* out, int out_dtype, int out_stride,
@@ -839,30 +839,26 @@ LLM_EXPORT int llm_min_gru(float* z, float* u, float* g, int stride, const float
                            cudaStream_t stream) {
   if (rows <= 0 || width <= 0) return 0;
   if (!single && !seg) return LLM_ERR_ARGUMENT;
-  const long long total = (long long)rows * width;
-  const int blocks = (int)((total + 255) / 256 < 2368 ? (total + 255) / 256 : 2368);
-  int rc = launch_pdl(min_gru_gates_kernel, blocks, 256, 0, stream, z, u, g, stride, bz, bx, total, width);
-  if (rc) return rc;
   if (!single) {
     const dim3 grid(n_slots, (width + 31) / 32);
     if (out_dtype == LLM_F32)
       return launch_pdl(min_gru_runs_kernel<float>, grid, GRU_WARPS * 32, 0, stream, (const float*)z,
-                        (const float*)u, (const float*)g, stride, state, state_stride, (float*)out, out_stride,
-                        seg, width);
+                        (const float*)u, (const float*)g, stride, bz, bx, state, state_stride, (float*)out,
+                        out_stride, seg, width);
     if (out_dtype == LLM_BF16)
       return launch_pdl(min_gru_runs_kernel<bf16>, grid, GRU_WARPS * 32, 0, stream, (const float*)z,
-                        (const float*)u, (const float*)g, stride, state, state_stride, (bf16*)out, out_stride, seg,
-                        width);
+                        (const float*)u, (const float*)g, stride, bz, bx, state, state_stride, (bf16*)out,
+                        out_stride, seg, width);
     return LLM_ERR_UNSUPPORTED;
   }
   const dim3 grid(rows, (width + 127) / 128);
   if (out_dtype == LLM_F32)
-    return launch_pdl(min_gru_scan_kernel<float>, grid, 128, 0, stream, (const float*)z, (const float*)u,
-                      (const float*)g, stride, state, state_stride, (float*)out, out_stride, row_slot, seg, single,
+    return launch_pdl(min_gru_token_kernel<float>, grid, 128, 0, stream, (const float*)z, (const float*)u,
+                      (const float*)g, stride, bz, bx, state, state_stride, (float*)out, out_stride, row_slot,
                       width);
   if (out_dtype == LLM_BF16)
-    return launch_pdl(min_gru_scan_kernel<bf16>, grid, 128, 0, stream, (const float*)z, (const float*)u,
-                      (const float*)g, stride, state, state_stride, (bf16*)out, out_stride, row_slot, seg, single,
+    return launch_pdl(min_gru_token_kernel<bf16>, grid, 128, 0, stream, (const float*)z, (const float*)u,
+                      (const float*)g, stride, bz, bx, state, state_stride, (bf16*)out, out_stride, row_slot,
                       width);
   return LLM_ERR_UNSUPPORTED;
 }

@@ -535,7 +535,7 @@ def min_gru(z: torch.Tensor, u: torch.Tensor, g: torch.Tensor, z_bias: Optional[
     """Per request and channel ``S <- (1 - s) S + s c`` over the rows of the step in order, with
     ``s = sigmoid(z + z_bias)`` and the candidate ``c = w + 1/2`` where ``w = u + u_bias >= 0``,
     ``sigmoid(w)`` elsewhere; ``out = S * silu(g)``.  z, u, g: float32 column ranges of one
-    matrix (equal row strides; they are overwritten); state float32 [slots, >= channels],
+    matrix (equal row strides); state float32 [slots, >= channels],
     carried from step to step; out [rows, channels].  ``seg``: the table of
     :func:`segment_table`, or None when every row is a request of its own."""
     _cuda(z, u, g, z_bias, u_bias, state, out, row_slot, seg)
