@@ -92,6 +92,12 @@ CONFIGS: Dict[str, dict] = {
                                    pool=4, rot=64),
                           attention(heads=8, kv_heads=2, dim=128, vdim=128, size=13, keep=6,
                                     mlp=dense(48))], width=64, vocab=80),
+    # keys shorter than values whose size the tensor-core kernels have: the cache's rows are the
+    # values', the queries and keys are padded
+    "keys_shorter": config([parallel(width=20, heads=4, kv_heads=2, dim=48, vdim=64, conv=3, size=11,
+                                     pool=3, rot=12),
+                            attention(heads=2, kv_heads=2, dim=32, vdim=64, size=9, keep=5,
+                                      mlp=dense(56))], width=72, vocab=70),
     # all of them, in an order of their own
     "mix": config([attention(size=21, keep=4, mlp=moe()),
                    parallel(mlp=moe(experts=4, top=2, identity=1)),
