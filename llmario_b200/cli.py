@@ -63,9 +63,17 @@ PEMOLORN_PRESETS = {"pemolorn-0.6b": ("qwen3-0.6b", 28), "pemolorn-8b": ("qwen3-
                     "pemolorn-tiny": ("tiny-b", 4)}
 
 
+# Pavatar models of the same sizes (random weights): layers repeating (gated delta rule,
+# attention with blended values, attention beside a gated delta rule, attention), each with
+# routed experts without a gate.
+PAVATAR_PRESETS = {"pavatar-0.6b": ("qwen3-0.6b", 28), "pavatar-8b": ("qwen3-8b", 36),
+                   "pavatar-tiny": ("tiny-b", 4)}
+
+
 def is_preset(name: str) -> bool:
     return name.lower() in PRESETS or name.lower() in VUNASUN_PRESETS \
-        or name.lower() in RUNIDRA_PRESETS or name.lower() in PEMOLORN_PRESETS
+        or name.lower() in RUNIDRA_PRESETS or name.lower() in PEMOLORN_PRESETS \
+        or name.lower() in PAVATAR_PRESETS
 
 
 def preset_config(name: str, num_layers: Optional[int] = None):
@@ -99,6 +107,17 @@ def preset_config(name: str, num_layers: Optional[int] = None):
                                    p["num_attention_heads"], p["num_key_value_heads"],
                                    p["head_dim"], int(num_layers or layers), p["vocab_size"],
                                    window=24 if tiny else 1024, pool=8 if tiny else 64)
+
+    if name.lower() in PAVATAR_PRESETS:
+        from .config.pavatar import sized_like as pavatar_sized_like
+
+        base, layers = PAVATAR_PRESETS[name.lower()]
+        p = PRESETS[base]
+        tiny = base.startswith("tiny")
+        return pavatar_sized_like(p["hidden_size"], p["intermediate_size"],
+                                  p["num_attention_heads"], p["num_key_value_heads"],
+                                  p["head_dim"], int(num_layers or layers), p["vocab_size"],
+                                  rank=8 if tiny else 64)
 
     raw = dict(PRESETS[name.lower()], architectures=["Qwen3ForCausalLM"], model_type="qwen3")
     if num_layers:
@@ -272,7 +291,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
                                  "one B200: token ids in, token ids out")
     sub = ap.add_subparsers(dest="cmd", required=True)
     run = sub.add_parser("run", help="generate from a prompt of token ids")
-    run.add_argument("model", help="model folder, or a preset name: " + ", ".join(list(PRESETS) + list(VUNASUN_PRESETS) + list(RUNIDRA_PRESETS) + list(PEMOLORN_PRESETS)))
+    run.add_argument("model", help="model folder, or a preset name: " + ", ".join(list(PRESETS) + list(VUNASUN_PRESETS) + list(RUNIDRA_PRESETS) + list(PEMOLORN_PRESETS) + list(PAVATAR_PRESETS)))
     run.add_argument("--tokens", default=None, help="comma-separated prompt token ids")
     run.add_argument("--prompt-len", type=int, default=16,
                      help="without --tokens: this many random ids")

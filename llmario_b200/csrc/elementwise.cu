@@ -5,10 +5,10 @@ int g_llm_pdl = 1;
 int g_llm_after_rotation = 0;
 LLM_EXPORT void llm_set_pdl(int on) { g_llm_pdl = on ? 1 : 0; }
 
-// x[t][:] = table[token[t]][:]   (residual stream is 32-bit in every mode)
+// x[t][:] = table[token[t]][:] * scale   (residual stream is 32-bit in every mode)
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
-                             float* __restrict__ x, int width, int vocab, int* __restrict__ err) {
+                             float* __restrict__ x, int width, int vocab, int* __restrict__ err, float scale) {
   // The first kernel of a step's layers waits BEFORE it lets its dependents start: no kernel
   // after it can begin, not even the part before its own wait, until everything ahead of the
   // embedding (the step's token, position and block-table updates) is complete.  Kernels of the
@@ -23,18 +23,25 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict
     return;
   }
   const T* row = table + (size_t)tok * width;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) x[(size_t)t * width + i] = to_f32(row[i]);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) x[(size_t)t * width + i] = to_f32(row[i]) * scale;
+}
+
+LLM_EXPORT int llm_embed_scaled(const int* tokens, const void* table, int table_dtype, float* x, int rows,
+                                int width, int vocab, int* err_flag, float scale, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int threads = width >= 1024 ? 256 : 128;
+  if (table_dtype == LLM_F32)
+    return launch_pdl(embed_kernel<float>, rows, threads, 0, stream, tokens, (const float*)table, x, width, vocab,
+                      err_flag, scale);
+  if (table_dtype == LLM_BF16)
+    return launch_pdl(embed_kernel<bf16>, rows, threads, 0, stream, tokens, (const bf16*)table, x, width, vocab,
+                      err_flag, scale);
+  return LLM_ERR_UNSUPPORTED;
 }
 
 LLM_EXPORT int llm_embed(const int* tokens, const void* table, int table_dtype, float* x, int rows,
                          int width, int vocab, int* err_flag, cudaStream_t stream) {
-  if (rows <= 0) return 0;
-  const int threads = width >= 1024 ? 256 : 128;
-  if (table_dtype == LLM_F32)
-    return launch_pdl(embed_kernel<float>, rows, threads, 0, stream, tokens, (const float*)table, x, width, vocab, err_flag);
-  if (table_dtype == LLM_BF16)
-    return launch_pdl(embed_kernel<bf16>, rows, threads, 0, stream, tokens, (const bf16*)table, x, width, vocab, err_flag);
-  return LLM_ERR_UNSUPPORTED;
+  return llm_embed_scaled(tokens, table, table_dtype, x, rows, width, vocab, err_flag, 1.f, stream);
 }
 
 // y[r][:] = x[src(r)][:] * rsqrt(mean(x^2) + eps) * w[:]    sums and scale in 32-bit.
@@ -536,5 +543,36 @@ LLM_EXPORT int llm_head_gate(void* out, int dtype, float* gate, int gate_stride,
     return launch_pdl(head_gate_kernel<float>, blocks, 128, 0, stream, (float*)out, gate, gate_stride, rows, H, hd, clear);
   if (dtype == LLM_BF16)
     return launch_pdl(head_gate_kernel<bf16>, blocks, 128, 0, stream, (bf16*)out, gate, gate_stride, rows, H, hd, clear);
+  return LLM_ERR_UNSUPPORTED;
+}
+
+// out[r][c] *= sigmoid(gate[r * gate_stride + c]): one gate per channel on the output of
+// attention, in 32-bit, rounded once.  With `clear` the gates that were read are zeroed.
+template <typename T>
+__global__ void channel_gate_kernel(T* __restrict__ out, float* __restrict__ gate, int gate_stride, int cols,
+                                    long long total, int clear) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / cols;
+    float* gp = gate + r * gate_stride + (i - r * cols);
+    const float z = *gp;
+    if (clear) *gp = 0.f;
+    out[i] = from_f32<T>(to_f32(out[i]) / (1.f + expf(-z)));
+  }
+}
+
+LLM_EXPORT int llm_channel_gate(void* out, int dtype, float* gate, int gate_stride, int rows, int cols, int clear,
+                                cudaStream_t stream) {
+  const long long total = (long long)rows * cols;
+  if (total <= 0) return 0;
+  const int blocks = (int)((total + 255) / 256 < 4736 ? (total + 255) / 256 : 4736);
+  if (dtype == LLM_F32)
+    return launch_pdl(channel_gate_kernel<float>, blocks, 256, 0, stream, (float*)out, gate, gate_stride, cols, total,
+                      clear);
+  if (dtype == LLM_BF16)
+    return launch_pdl(channel_gate_kernel<bf16>, blocks, 256, 0, stream, (bf16*)out, gate, gate_stride, cols, total,
+                      clear);
   return LLM_ERR_UNSUPPORTED;
 }

@@ -24,9 +24,13 @@ constexpr int MAX_TOP = 16;
 // mode 0: the k-th choice is the largest logit not chosen before (the lowest index among equals);
 // the weights are a softmax in which only the chosen logits take part.  mode 1: scores are the
 // softmax over all E outputs; the choice goes by score + corr[e] (the same tie rule), the weight
-// of a chosen expert is its score, not renormalised.
+// of a chosen expert is its score, not renormalised.  mode 2: as mode 1, but the weights are the
+// chosen scores over their sum (+ 1e-20), times `wscale`.
 __device__ __forceinline__ void choose_row(const float* zr, int E, int top, int mode, const float* __restrict__ corr,
-                                           int lane, int* __restrict__ ids, float* __restrict__ wts) {
+                                           int lane, int* __restrict__ ids, float* __restrict__ wts,
+                                           float wscale = 1.f) {
+  const bool renorm = mode == 2;
+  if (renorm) mode = 1;
   float zmax = 0.f, inv_sum = 1.f;
   if (mode == 1) {
     float mx = -INFINITY;
@@ -57,9 +61,15 @@ __device__ __forceinline__ void choose_row(const float* zr, int E, int top, int 
   }
   if (lane == 0) {
     if (mode == 1) {
+      float chosen = 0.f;
       for (int k = 0; k < top; ++k) {
         ids[k] = pick[k];
         wts[k] = expf(zr[pick[k]] - zmax) * inv_sum;
+        chosen += wts[k];
+      }
+      if (renorm) {
+        const float f = wscale / (chosen + 1e-20f);
+        for (int k = 0; k < top; ++k) wts[k] *= f;
       }
       return;
     }
@@ -75,12 +85,14 @@ __device__ __forceinline__ void choose_row(const float* zr, int E, int top, int 
 // One warp per row.
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ z, int z_stride, int rows, int E,
                                                         int top, int mode, const float* __restrict__ corr,
-                                                        int* __restrict__ ids, float* __restrict__ wts) {
+                                                        int* __restrict__ ids, float* __restrict__ wts,
+                                                        float wscale) {
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (r >= rows) return;
-  choose_row(z + (size_t)r * z_stride, E, top, mode, corr, lane, ids + (size_t)r * top, wts + (size_t)r * top);
+  choose_row(z + (size_t)r * z_stride, E, top, mode, corr, lane, ids + (size_t)r * top, wts + (size_t)r * top,
+             wscale);
 }
 
 
@@ -94,7 +106,8 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ h
                                                          const float* __restrict__ b, float* __restrict__ z_out,
                                                          int z_stride, int rows, int width, int E, int n_out,
                                                          int top, int mode, const float* __restrict__ corr,
-                                                         int* __restrict__ ids, float* __restrict__ wts) {
+                                                         int* __restrict__ ids, float* __restrict__ wts,
+                                                         float wscale) {
   extern __shared__ float rs[];        // h[R][width], z[R][n_out]
   float* h_s = rs;
   float* z_s = rs + (size_t)R * width;
@@ -143,7 +156,7 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ h
   __syncthreads();
   if (warp >= R || r0 + warp >= rows) return;
   const int r = r0 + warp;
-  choose_row(z_s + warp * n_out, E, top, mode, corr, lane, ids + (size_t)r * top, wts + (size_t)r * top);
+  choose_row(z_s + warp * n_out, E, top, mode, corr, lane, ids + (size_t)r * top, wts + (size_t)r * top, wscale);
 }
 
 template <typename T> __device__ __forceinline__ float dot_row(const T* __restrict__ w, const float* __restrict__ x,
@@ -174,7 +187,8 @@ template <> __device__ __forceinline__ float dot_row<bf16>(const bf16* __restric
 }
 
 // grid (rows * top, ff tiles of 8); a block stages its row of h in shared memory, a warp makes
-// two features.  gate_up: [E][2 ff][width], gate rows first.
+// two features.  gate_up: [E][2 ff][width], gate rows first; kind 3 (an expert without a gate,
+// act = max(W_up h, 0)^2): [E][ff][width].
 template <typename T>
 __global__ void __launch_bounds__(128) moe_gate_up_rows_kernel(const T* __restrict__ h, const T* __restrict__ gate_up,
                                                                const int* __restrict__ ids, T* __restrict__ act,
@@ -189,9 +203,14 @@ __global__ void __launch_bounds__(128) moe_gate_up_rows_kernel(const T* __restri
   for (int i = threadIdx.x; i < width; i += blockDim.x) h_s[i] = to_f32(h[(size_t)r * width + i]);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const T* we = gate_up + (size_t)e * 2 * ff * width;
+  const T* we = gate_up + (size_t)e * (kind == 3 ? 1 : 2) * ff * width;
   for (int f = blockIdx.y * 8 + warp; f < min(ff, blockIdx.y * 8 + 8); f += 4) {
     const float g = dot_row<T>(we + (size_t)f * width, h_s, width, lane);
+    if (kind == 3) {
+      const float p = fmaxf(g, 0.f);
+      if (lane == 0) act[(size_t)item * ff + f] = from_f32<T>(p * p);
+      continue;
+    }
     const float u = dot_row<T>(we + (size_t)(ff + f) * width, h_s, width, lane);
     if (lane == 0) {
       float y;
@@ -365,11 +384,12 @@ LLM_EXPORT int llm_moe_combine(const float* d, const int* pos, const float* wts,
 // The router: z_out[r][0:n_out] = w h_r + b (w float32 [n_out][width], the first E rows the
 // experts'), ids / wts the `top` chosen experts of every row and their weights.
 // mode and corr: see choose_row.
-LLM_EXPORT int llm_moe_router(const void* h, int dtype, const float* w, const float* b, float* z_out, int z_stride,
-                              int rows, int width, int E, int n_out, int top, int mode, const float* corr,
-                              int* ids, float* wts, cudaStream_t stream) {
+// mode, corr and wscale: see choose_row.
+LLM_EXPORT int llm_moe_router_scaled(const void* h, int dtype, const float* w, const float* b, float* z_out,
+                                     int z_stride, int rows, int width, int E, int n_out, int top, int mode,
+                                     const float* corr, int* ids, float* wts, float wscale, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (top < 1 || top > MAX_TOP || top > E || n_out < E) return LLM_ERR_UNSUPPORTED;
+  if (top < 1 || top > MAX_TOP || top > E || n_out < E || mode < 0 || mode > 2) return LLM_ERR_UNSUPPORTED;
   if ((size_t)(width + n_out) * 4 > 200 * 1024) return LLM_ERR_UNSUPPORTED;
   // many rows: four to a block, so that a block reads the router's rows once for four tokens
   const bool four = rows >= 256 && (size_t)4 * (width + n_out) * 4 <= 200 * 1024;
@@ -381,7 +401,7 @@ LLM_EXPORT int llm_moe_router(const void* h, int dtype, const float* w, const fl
     if (smem > 48 * 1024)                                                                                      \
       cudaFuncSetAttribute(moe_router_kernel<T, RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
     return launch_pdl(moe_router_kernel<T, RR>, blocks, 256, smem, stream, (const T*)h, w, b, z_out, z_stride, \
-                      rows, width, E, n_out, top, mode, corr, ids, wts);                                       \
+                      rows, width, E, n_out, top, mode, corr, ids, wts, wscale);                               \
   } while (0)
   if (dtype == LLM_F32) {
     if (four) ROUTER(float, 4);
@@ -395,16 +415,28 @@ LLM_EXPORT int llm_moe_router(const void* h, int dtype, const float* w, const fl
   return LLM_ERR_UNSUPPORTED;
 }
 
+LLM_EXPORT int llm_moe_router(const void* h, int dtype, const float* w, const float* b, float* z_out, int z_stride,
+                              int rows, int width, int E, int n_out, int top, int mode, const float* corr,
+                              int* ids, float* wts, cudaStream_t stream) {
+  return llm_moe_router_scaled(h, dtype, w, b, z_out, z_stride, rows, width, E, n_out, top, mode, corr, ids, wts,
+                               1.f, stream);
+}
+
+LLM_EXPORT int llm_moe_route_scaled(const float* z, int z_stride, int rows, int E, int top, int mode,
+                                    const float* corr, int* ids, float* wts, float wscale, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (top < 1 || top > MAX_TOP || top > E || mode < 0 || mode > 2) return LLM_ERR_UNSUPPORTED;
+  return launch_pdl(moe_route_kernel, (rows + 3) / 4, 128, 0, stream, z, z_stride, rows, E, top, mode, corr, ids,
+                    wts, wscale);
+}
+
 LLM_EXPORT int llm_moe_route(const float* z, int z_stride, int rows, int E, int top, int mode, const float* corr,
                              int* ids, float* wts, cudaStream_t stream) {
-  if (rows <= 0) return 0;
-  if (top < 1 || top > MAX_TOP || top > E || mode < 0 || mode > 1) return LLM_ERR_UNSUPPORTED;
-  return launch_pdl(moe_route_kernel, (rows + 3) / 4, 128, 0, stream, z, z_stride, rows, E, top, mode, corr, ids,
-                    wts);
+  return llm_moe_route_scaled(z, z_stride, rows, E, top, mode, corr, ids, wts, 1.f, stream);
 }
 
 // E: experts with matrices (a pair whose expert is not one of them is left out); kind 0: silu(g) u,
-// 2: the clamped form with `limit` (see activations.cu)
+// 2: the clamped form with `limit` (see activations.cu), 3: no gate, max(u, 0)^2 with gate_up [E][ff][width]
 LLM_EXPORT int llm_moe_gate_up_rows(const void* h, const void* gate_up, const int* ids, void* act, int dtype,
                                     int rows, int width, int ff, int top, int E, int kind, float limit,
                                     cudaStream_t stream) {

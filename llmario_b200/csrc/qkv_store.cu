@@ -10,6 +10,9 @@
 //   angles (cos and sin per (row, i) made once per step); the other channels pass.
 //   q goes out as [rows][Hq][hd] in the step's type, keys and values into the pages of the row's
 //   request; hd >= max(d, dv) is the cache's row, the channels behind d (dv) are written as zeros.
+//   temperature: the queries of position p are multiplied by 1 + coef * ln(floor((p + 1) / every) + 1).
+//   blend: the value that is stored is (1 - lambda) v + lambda v0, v0 another layer's values of
+//   the same rows (32-bit, as projected).
 //
 // llm_pool_blocks, one block per (row, key head): a row whose position ends a block of P tokens
 // (pos % P == P - 1) writes entry pos / P of the pooled cache: the means of the block's P cached
@@ -30,6 +33,9 @@ struct StoreArgs {
   int table_stride, page_size;
   int rows, Hq, Hkv, d, dv, hd, rot, norm, has_kv;
   float eps;
+  float temp_coef; int temp_every;     // query temperature by position (every 0: none)
+  const float* v0; int v0_stride;      // values to blend in ([rows][Hkv * dv]) or null
+  float blend;
 };
 
 __device__ __forceinline__ void store2(float* dst, float a, float b) { *reinterpret_cast<float2*>(dst) = make_float2(a, b); }
@@ -68,6 +74,8 @@ __global__ void __launch_bounds__(256) qkv_store_kernel(const StoreArgs a) {
     }
   }
   const int pos = a.row_pos[r];
+  const float temp = a.temp_every > 0
+      ? 1.f + a.temp_coef * logf((float)((pos + 1) / a.temp_every + 1)) : 1.f;
   long long page_off = 0;
   if (a.has_kv) {
     const int page = a.table[(size_t)a.row_slot[r] * a.table_stride + pos / a.page_size];
@@ -79,15 +87,21 @@ __global__ void __launch_bounds__(256) qkv_store_kernel(const StoreArgs a) {
     if (item >= a.Hq + a.Hkv) {                    // a value head: a copy, padded with zeros
       const int g = item - a.Hq - a.Hkv;
       const float* src = a.v + (size_t)r * a.v_stride + (size_t)g * a.dv;
+      const float* mix = a.v0 ? a.v0 + (size_t)r * a.v0_stride + (size_t)g * a.dv : nullptr;
+      const float keep = 1.f - a.blend;
       T* dst = (T*)a.v_cache + page_off + ((long long)g * a.page_size + pos % a.page_size) * a.hd;
-      if (PAIRS) {
+      if (PAIRS && !mix) {
         for (int c = 2 * lane; c < a.hd; c += 64) {
           float2 x = make_float2(0.f, 0.f);
           if (c < a.dv) x = *reinterpret_cast<const float2*>(src + c);
           store2(dst + c, x.x, x.y);
         }
       } else {
-        for (int c = lane; c < a.hd; c += 32) dst[c] = from_f32<T>(c < a.dv ? src[c] : 0.f);
+        for (int c = lane; c < a.hd; c += 32) {
+          float x = c < a.dv ? src[c] : 0.f;
+          if (mix && c < a.dv) x = fmaf(a.blend, mix[c], keep * x);
+          dst[c] = from_f32<T>(x);
+        }
       }
       continue;
     }
@@ -101,6 +115,7 @@ __global__ void __launch_bounds__(256) qkv_store_kernel(const StoreArgs a) {
       for (int c = lane; c < a.d; c += 32) s = fmaf(src[c], src[c], s);
       scale = rsqrtf(warp_sum(s) / (float)a.d + a.eps);
     }
+    if (is_q) scale *= temp;
     if (w && a.norm == 2) w += (size_t)h * a.d;
     if (!a.norm) w = nullptr;
     T* dst = is_q ? (T*)a.q_out + ((size_t)r * a.Hq + h) * a.hd
@@ -184,13 +199,15 @@ __global__ void __launch_bounds__(1024) pool_blocks_kernel(
 }
 }  // namespace
 
-LLM_EXPORT int llm_qkv_store(const float* q, int q_stride, const float* k, int k_stride, const float* v,
-                             int v_stride, const float* q_w, const float* k_w, const float* cos_sin, void* q_out,
-                             void* k_cache, void* v_cache, int dtype, long long page_stride, const int* table,
-                             int table_stride, const int* row_slot, const int* row_pos, int rows, int Hq, int Hkv,
-                             int d, int dv, int hd, int rot, int norm, float eps, int page_size, int has_kv,
-                             cudaStream_t stream) {
+LLM_EXPORT int llm_qkv_store_mix(const float* q, int q_stride, const float* k, int k_stride, const float* v,
+                                 int v_stride, const float* q_w, const float* k_w, const float* cos_sin,
+                                 void* q_out, void* k_cache, void* v_cache, int dtype, long long page_stride,
+                                 const int* table, int table_stride, const int* row_slot, const int* row_pos,
+                                 int rows, int Hq, int Hkv, int d, int dv, int hd, int rot, int norm, float eps,
+                                 int page_size, int has_kv, float temp_coef, int temp_every, const float* v0,
+                                 int v0_stride, float blend, cudaStream_t stream) {
   if (rows <= 0) return 0;
+  if (temp_every < 0) return LLM_ERR_ARGUMENT;
   if (d <= 0 || dv <= 0 || hd < d || hd < dv || rot < 0 || rot > d || (rot & 1) || norm < 0 || norm > 2)
     return LLM_ERR_ARGUMENT;
   if (rot > 0 && !cos_sin) return LLM_ERR_ARGUMENT;
@@ -201,6 +218,8 @@ LLM_EXPORT int llm_qkv_store(const float* q, int q_stride, const float* k, int k
   a.page_stride = page_stride, a.table = table, a.row_slot = row_slot, a.row_pos = row_pos;
   a.table_stride = table_stride, a.page_size = page_size, a.rows = rows, a.Hq = Hq, a.Hkv = Hkv, a.d = d,
   a.dv = dv, a.hd = hd, a.rot = rot, a.norm = norm, a.has_kv = has_kv, a.eps = eps;
+  a.temp_coef = temp_coef, a.temp_every = temp_every, a.v0 = has_kv ? v0 : nullptr, a.v0_stride = v0_stride,
+  a.blend = blend;
   const int heads = Hq + (has_kv ? 2 * Hkv : 0);
   const int threads = heads >= 8 ? 256 : heads >= 4 ? 128 : 64;
   // few rows: the heads of a row are shared out to several blocks, so that the step fills the GPU
@@ -223,6 +242,17 @@ LLM_EXPORT int llm_qkv_store(const float* q, int q_stride, const float* k, int k
   else return LLM_ERR_UNSUPPORTED;
 #undef STORE_GO
   return launched_many_blocks(rc, (long long)rows * shares);
+}
+
+LLM_EXPORT int llm_qkv_store(const float* q, int q_stride, const float* k, int k_stride, const float* v,
+                             int v_stride, const float* q_w, const float* k_w, const float* cos_sin, void* q_out,
+                             void* k_cache, void* v_cache, int dtype, long long page_stride, const int* table,
+                             int table_stride, const int* row_slot, const int* row_pos, int rows, int Hq, int Hkv,
+                             int d, int dv, int hd, int rot, int norm, float eps, int page_size, int has_kv,
+                             cudaStream_t stream) {
+  return llm_qkv_store_mix(q, q_stride, k, k_stride, v, v_stride, q_w, k_w, cos_sin, q_out, k_cache, v_cache, dtype,
+                           page_stride, table, table_stride, row_slot, row_pos, rows, Hq, Hkv, d, dv, hd, rot, norm,
+                           eps, page_size, has_kv, 0.f, 0, nullptr, 0, 0.f, stream);
 }
 
 LLM_EXPORT int llm_pool_blocks(const void* k_cache, const void* v_cache, long long page_stride, const int* table,

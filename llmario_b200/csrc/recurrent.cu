@@ -4,7 +4,9 @@
 // the short causal convolution that some of them put in front of it, and the gated group norm
 // that follows it.  Gated linear attention (a decay per key channel) and state-space mixers of
 // the Mamba-2 kind (a scalar decay per head, keys and queries shared by the heads of a group,
-// values scaled by the step size) are both this recurrence; which one runs is data.
+// values scaled by the step size) are both this recurrence; which one runs is data.  So is the
+// gated delta rule, whose write is the error of the state's own answer for the key:
+//   S <- diag(a_t) S;  u = b_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t.
 //
 // Everything here is 32-bit: the inputs are the 32-bit results of the projections, the state
 // lives in 32-bit floats in the request's state slot, decays and step sizes are made here from
@@ -55,6 +57,7 @@ enum DecayKind : int {
   DECAY_SCALAR_INPUT = 3,  // a = d, v is scaled by d2    d, d2 per (row, head): a decay and an input
                            //                             weight that another kernel has made
 };
+// (With the delta rule DECAY_RATE_STEP leaves v as it is: the step only makes the decay.)
 
 struct ScanArgs {
   const float* q; int q_stride;          // q[row * q_stride + g * K + i], g = h / (H / G)
@@ -72,6 +75,10 @@ struct ScanArgs {
   float* out; int out_stride;            // out[row * out_stride + h * V + j]
   const int* seg; const int* row_slot;
   int single, H, G, K, V, kind;
+  // the delta rule: beta[row * beta_stride + h] is the write strength before its sigmoid;
+  // `unit`: q and k of every head are divided by sqrt(sum of squares + unit_floor) first
+  const float* beta; int beta_stride;
+  int unit; float unit_floor;
 };
 
 constexpr int SCAN_THREADS = 128;
@@ -96,7 +103,14 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 // for 32 lanes.  The tokens' q, k and decay arguments come into shared memory a chunk of tokens
 // at a time by asynchronous copies, two chunks in flight: while one chunk is walked the next is
 // on its way.
-template <int L, int NF, bool VEC>
+//
+// DELTA: the gated delta rule.  Per token the state is decayed, its answers for the key and for
+// the query are summed in one pass (two sets of partial sums), the write u = b (v - S^T k) is
+// made where the key's sums end up, handed back to the L lanes of the group, and added as
+// k u^T; the output is the decayed state's answer for the query plus u (k . q), which is what
+// the written state answers.  q and k are made unit vectors (and q scaled) in shared memory once
+// per token, with k . q beside them.
+template <int L, int NF, bool VEC, bool DELTA>
 __global__ void __launch_bounds__(SCAN_THREADS) linear_recurrence_kernel(const ScanArgs a) {
   constexpr int KP = 4 * L * NF;                            // key channels, padded
   constexpr int GROUPS = 32 / L;                            // column groups of a warp
@@ -108,6 +122,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_recurrence_kernel(const S
   __shared__ __align__(16) float v_s[2][TC][COLS];
   __shared__ float d_s[2][TC];          // scalar decay: its argument, then the decay itself
   __shared__ float w_s[2][TC];          // DECAY_SCALAR_INPUT: the input weight
+  __shared__ float b_s[2][DELTA ? TC : 1];      // the delta rule: write strength, and k . q
+  __shared__ float kq_s[2][DELTA ? TC : 1];
   pdl_trigger();
   pdl_wait();
   const int h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -172,6 +188,9 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_recurrence_kernel(const S
         cp_async4(&d_s[st][tt], a.d + (size_t)(t0 + tt) * a.d_stride + h);
         if (a.kind == DECAY_SCALAR_INPUT) cp_async4(&w_s[st][tt], a.d2 + (size_t)(t0 + tt) * a.d_stride + h);
       }
+    if (DELTA)
+      for (int tt = tid; tt < n_tok; tt += SCAN_THREADS)
+        cp_async4(&b_s[st][tt], a.beta + (size_t)(t0 + tt) * a.beta_stride + h);
     cp_async_commit();
   };
 
@@ -224,13 +243,41 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_recurrence_kernel(const S
         v_s[st][tt][cc] *= w_s[st][tt];
       }
     } else {
-      for (int idx = tid; idx < n_tok * COLS; idx += SCAN_THREADS) {
-        const int tt = idx / COLS, cc = idx - tt * COLS;
-        v_s[st][tt][cc] *= softplus_f(d_s[st][tt] + bias);
+      if (!DELTA) {
+        for (int idx = tid; idx < n_tok * COLS; idx += SCAN_THREADS) {
+          const int tt = idx / COLS, cc = idx - tt * COLS;
+          v_s[st][tt][cc] *= softplus_f(d_s[st][tt] + bias);
+        }
+        __syncthreads();
       }
-      __syncthreads();
       for (int tt = tid; tt < n_tok; tt += SCAN_THREADS)
         d_s[st][tt] = expf(-rate * softplus_f(d_s[st][tt] + bias));
+    }
+    if (DELTA) {
+      // a warp per token: unit vectors, the query's scale, k . q, the write strength
+      for (int tt = warp; tt < n_tok; tt += SCAN_THREADS / 32) {
+        float sq = 0.f, sk = 0.f;
+        if (a.unit) {
+          for (int i = lane; i < K; i += 32) {
+            sq = fmaf(q_s[st][tt][i], q_s[st][tt][i], sq);
+            sk = fmaf(k_s[st][tt][i], k_s[st][tt][i], sk);
+          }
+          sq = warp_sum(sq), sk = warp_sum(sk);
+        }
+        const float fq = (a.unit ? 1.0f / sqrtf(sq + a.unit_floor) : 1.f) * q_scale;
+        const float fk = a.unit ? 1.0f / sqrtf(sk + a.unit_floor) : 1.f;
+        float dot = 0.f;
+        for (int i = lane; i < K; i += 32) {
+          const float qv = q_s[st][tt][i] * fq, kv = k_s[st][tt][i] * fk;
+          q_s[st][tt][i] = qv, k_s[st][tt][i] = kv;
+          dot = fmaf(qv, kv, dot);
+        }
+        dot = warp_sum(dot);
+        if (lane == 0) {
+          kq_s[st][tt] = dot;
+          b_s[st][tt] = 1.f / (1.f + expf(-b_s[st][tt]));
+        }
+      }
     }
     __syncthreads();
     // ---- the tokens of the chunk, one after the other
@@ -239,6 +286,58 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_recurrence_kernel(const S
       const float4 vv = *reinterpret_cast<const float4*>(&v_s[st][tt][c0]);
       const float a1 = VEC ? 1.f : d_s[st][tt];
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      if (DELTA) {
+        float ack[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int n = 0; n < NF; ++n) {
+          const float4 qq = *reinterpret_cast<const float4*>(&q_s[st][tt][4 * (li + L * n)]);
+          const float4 kk = *reinterpret_cast<const float4*>(&k_s[st][tt][4 * (li + L * n)]);
+          float4 aa = make_float4(a1, a1, a1, a1);
+          if (VEC) aa = *reinterpret_cast<const float4*>(&a_s[st][tt][4 * (li + L * n)]);
+          const float qe[4] = {qq.x, qq.y, qq.z, qq.w}, ke[4] = {kk.x, kk.y, kk.z, kk.w};
+          const float ae[4] = {aa.x, aa.y, aa.z, aa.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              s[n][e][c] *= ae[e];
+              ack[c] = fmaf(s[n][e][c], ke[e], ack[c]);
+              acc[c] = fmaf(s[n][e][c], qe[e], acc[c]);
+            }
+        }
+        // both sets of sums over the L lanes of the group, as below
+        const float rk0 = __shfl_xor_sync(0xffffffffu, up1 ? ack[0] : ack[2], L / 2);
+        const float rk1 = __shfl_xor_sync(0xffffffffu, up1 ? ack[1] : ack[3], L / 2);
+        const float rq0 = __shfl_xor_sync(0xffffffffu, up1 ? acc[0] : acc[2], L / 2);
+        const float rq1 = __shfl_xor_sync(0xffffffffu, up1 ? acc[1] : acc[3], L / 2);
+        const float bk0 = (up1 ? ack[2] : ack[0]) + rk0, bk1 = (up1 ? ack[3] : ack[1]) + rk1;
+        const float bq0 = (up1 ? acc[2] : acc[0]) + rq0, bq1 = (up1 ? acc[3] : acc[1]) + rq1;
+        float sumk = (up2 ? bk1 : bk0) + __shfl_xor_sync(0xffffffffu, up2 ? bk0 : bk1, L / 4);
+        float sumq = (up2 ? bq1 : bq0) + __shfl_xor_sync(0xffffffffu, up2 ? bq0 : bq1, L / 4);
+#pragma unroll
+        for (int o = L / 8; o > 0; o >>= 1) {
+          sumk += __shfl_xor_sync(0xffffffffu, sumk, o);
+          sumq += __shfl_xor_sync(0xffffffffu, sumq, o);
+        }
+        // every lane now holds both sums of the column 2 up1 + up2 of its group
+        const float v_mine = up1 ? (up2 ? vv.w : vv.z) : (up2 ? vv.y : vv.x);
+        const float u_mine = b_s[st][tt] * (v_mine - sumk);
+        if (writer) a.out[(size_t)(t0 + tt) * a.out_stride + h * V + my_col] = fmaf(u_mine, kq_s[st][tt], sumq);
+        const int base = lane - li;
+        const float ue[4] = {__shfl_sync(0xffffffffu, u_mine, base), __shfl_sync(0xffffffffu, u_mine, base + L / 4),
+                             __shfl_sync(0xffffffffu, u_mine, base + L / 2),
+                             __shfl_sync(0xffffffffu, u_mine, base + L / 2 + L / 4)};
+#pragma unroll
+        for (int n = 0; n < NF; ++n) {
+          const float4 kk = *reinterpret_cast<const float4*>(&k_s[st][tt][4 * (li + L * n)]);
+          const float ke[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) s[n][e][c] = fmaf(ke[e], ue[c], s[n][e][c]);
+        }
+        continue;
+      }
 #pragma unroll
       for (int n = 0; n < NF; ++n) {
         const float4 qq = *reinterpret_cast<const float4*>(&q_s[st][tt][4 * (li + L * n)]);
@@ -289,9 +388,13 @@ template <int L, int NF>
 int launch_scan(const ScanArgs& a, int blocks_x, cudaStream_t stream) {
   constexpr int COLS = 4 * (32 / L) * (SCAN_THREADS / 32);
   const dim3 grid(blocks_x, a.H, (a.V + COLS - 1) / COLS);
-  if (a.kind == DECAY_RATE_STEP || a.kind == DECAY_SCALAR_INPUT)
-    return launch_pdl(linear_recurrence_kernel<L, NF, false>, grid, SCAN_THREADS, 0, stream, a);
-  return launch_pdl(linear_recurrence_kernel<L, NF, true>, grid, SCAN_THREADS, 0, stream, a);
+  const bool scalar = a.kind == DECAY_RATE_STEP || a.kind == DECAY_SCALAR_INPUT;
+  if (a.beta) {
+    if (scalar) return launch_pdl(linear_recurrence_kernel<L, NF, false, true>, grid, SCAN_THREADS, 0, stream, a);
+    return launch_pdl(linear_recurrence_kernel<L, NF, true, true>, grid, SCAN_THREADS, 0, stream, a);
+  }
+  if (scalar) return launch_pdl(linear_recurrence_kernel<L, NF, false, false>, grid, SCAN_THREADS, 0, stream, a);
+  return launch_pdl(linear_recurrence_kernel<L, NF, true, false>, grid, SCAN_THREADS, 0, stream, a);
 }
 
 // z[r][i] = sigmoid(z[r][i] + b[i])^c in place: the decay of gated linear attention from the
@@ -305,6 +408,17 @@ __global__ void bias_sigmoid_pow_kernel(float* __restrict__ z, const float* __re
        i += (long long)gridDim.x * blockDim.x) {
     const float x = z[i] + (b ? b[i % n] : 0.f);
     z[i] = expf(-c * softplus_f(-x));
+  }
+}
+
+__global__ void rate_decay_kernel(float* __restrict__ z, const float* __restrict__ rate_log,
+                                  const float* __restrict__ b, long long total, int n, int per) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % n);
+    z[i] = expf(-expf(rate_log[c / per]) * softplus_f(z[i] + (b ? b[c] : 0.f)));
   }
 }
 
@@ -403,17 +517,22 @@ __global__ void conv_history_kernel(const float* __restrict__ src, int src_strid
 //   y = o (+ skip[ch / head] * x)                        the recurrence's output, plus a direct path
 //   gate_first:  out = unit(y * silu(g)) * w             (the gate comes before the norm)
 //   otherwise:   out = unit(y) * w * silu(g)
+// (gate_sigmoid: sigmoid(g) in the place of silu(g))
 // unit(.) divides a group by its root mean square (eps inside the root); w is indexed by the
 // channel modulo w_period (a weight per channel, or one per position in a head shared by heads).
 // A thread keeps up to GN_KEEP of its values between the sum and the scaling; a group larger
 // than GN_KEEP * THREADS reads the rest twice.
 constexpr int GN_KEEP = 8;
+__device__ __forceinline__ float gate_f(float z, int sigmoid) {
+  const float sg = 1.f / (1.f + expf(-z));
+  return sigmoid ? sg : z * sg;
+}
 template <typename TOut, int THREADS>
 __global__ void __launch_bounds__(THREADS) gated_group_norm_kernel(
     const float* __restrict__ o, int o_stride, const float* __restrict__ x, int x_stride,
     const float* __restrict__ skip, int head, const float* __restrict__ g, int g_stride,
     const float* __restrict__ w, int w_period, TOut* __restrict__ out, int out_stride, int groups, int group,
-    float eps, int gate_first) {
+    float eps, int gate_first, int gate_sigmoid) {
   __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
@@ -424,7 +543,7 @@ __global__ void __launch_bounds__(THREADS) gated_group_norm_kernel(
   auto value = [&](int ch, float& gt) {
     float v = o[(size_t)r * o_stride + ch];
     if (skip) v = fmaf(skip[ch / head], x[(size_t)r * x_stride + ch], v);
-    gt = silu_f(g[(size_t)r * g_stride + ch]);
+    gt = gate_f(g[(size_t)r * g_stride + ch], gate_sigmoid);
     if (gate_first) v *= gt;
     return v;
   };
@@ -469,7 +588,7 @@ __global__ void __launch_bounds__(THREADS) gated_group_norm_vec_kernel(
     const float* __restrict__ o, int o_stride, const float* __restrict__ x, int x_stride,
     const float* __restrict__ skip, int head, const float* __restrict__ g, int g_stride,
     const float* __restrict__ w, int w_period, TOut* __restrict__ out, int out_stride, int groups, int group,
-    float eps, int gate_first) {
+    float eps, int gate_first, int gate_sigmoid) {
   constexpr int KEEP = 2;
   __shared__ float scratch[33];
   pdl_trigger();
@@ -484,7 +603,8 @@ __global__ void __launch_bounds__(THREADS) gated_group_norm_vec_kernel(
       v.x = fmaf(d, xv.x, v.x), v.y = fmaf(d, xv.y, v.y), v.z = fmaf(d, xv.z, v.z), v.w = fmaf(d, xv.w, v.w);
     }
     const float4 gv = *reinterpret_cast<const float4*>(g + (size_t)r * g_stride + ch);
-    gt = make_float4(silu_f(gv.x), silu_f(gv.y), silu_f(gv.z), silu_f(gv.w));
+    gt = make_float4(gate_f(gv.x, gate_sigmoid), gate_f(gv.y, gate_sigmoid), gate_f(gv.z, gate_sigmoid),
+                     gate_f(gv.w, gate_sigmoid));
     if (gate_first) v.x *= gt.x, v.y *= gt.y, v.z *= gt.z, v.w *= gt.w;
     return v;
   };
@@ -651,6 +771,16 @@ LLM_EXPORT int llm_segment_table(const int* row_slot, int rows, int* seg, int n_
   return launch_pdl(segment_table_kernel, 1, 256, 0, stream, row_slot, rows, seg, n_slots);
 }
 
+static int run_scan(ScanArgs& a, int rows, int n_requests, cudaStream_t stream) {
+  const int bx = a.single ? rows : n_requests;
+  const int K = a.K;
+  if (K <= 32) return launch_scan<8, 1>(a, bx, stream);
+  if (K <= 64) return launch_scan<16, 1>(a, bx, stream);
+  if (K <= 128) return launch_scan<32, 1>(a, bx, stream);
+  if (K <= 256) return launch_scan<32, 2>(a, bx, stream);
+  return launch_scan<32, 4>(a, bx, stream);
+}
+
 // The recurrence over the rows of a step (see the top of this file).  `single`: every row is a
 // request of its own; else `seg` is the table of llm_segment_table and `n_requests` the number of
 // requests that have rows in the step.  The state of a (slot, head) is V x K floats, the key
@@ -677,12 +807,50 @@ LLM_EXPORT int llm_linear_recurrence(const float* q, int q_stride, const float* 
   a.state = state, a.state_stride = state_stride, a.out = out, a.out_stride = out_stride;
   a.seg = seg, a.row_slot = row_slot;
   a.single = single, a.H = H, a.G = G, a.K = K, a.V = V, a.kind = kind;
-  const int bx = single ? rows : n_requests;
-  if (K <= 32) return launch_scan<8, 1>(a, bx, stream);
-  if (K <= 64) return launch_scan<16, 1>(a, bx, stream);
-  if (K <= 128) return launch_scan<32, 1>(a, bx, stream);
-  if (K <= 256) return launch_scan<32, 2>(a, bx, stream);
-  return launch_scan<32, 4>(a, bx, stream);
+  a.beta = nullptr, a.beta_stride = 0, a.unit = 0, a.unit_floor = 0.f;
+  return run_scan(a, rows, n_requests, stream);
+}
+
+// The gated delta rule over the rows of a step, with the state and the segments of the recurrence
+// above:  S <- diag(a_t) S;  u = sigmoid(beta_t) (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t.
+// kind DECAY_VECTOR: d [rows][H * K] is the decay itself; DECAY_RATE_STEP: d [rows][H] and
+// a = exp(-exp(p0[h]) softplus(d + p1[h])) for all key channels of head h.  beta [rows][H] is read
+// before its sigmoid.  `unit`: q and k of every head are divided by sqrt(sum of squares + floor)
+// first; q is then multiplied by q_scale.
+LLM_EXPORT int llm_delta_recurrence(const float* q, int q_stride, const float* k, int k_stride, const float* v,
+                                    int v_stride, const float* d, int d_stride, const float* beta,
+                                    int beta_stride, const float* p0, const float* p1, float q_scale, int unit,
+                                    float unit_floor, float* state, long long state_stride, float* out,
+                                    int out_stride, const int* seg, const int* row_slot, int rows,
+                                    int n_requests, int single, int H, int G, int K, int V, int kind,
+                                    cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (H <= 0 || G <= 0 || H % G || K <= 0 || V <= 0 || !beta) return LLM_ERR_ARGUMENT;
+  if (kind != DECAY_VECTOR && kind != DECAY_RATE_STEP) return LLM_ERR_ARGUMENT;
+  if (kind == DECAY_RATE_STEP && (!p0 || !p1)) return LLM_ERR_ARGUMENT;
+  if (!single && (!seg || n_requests <= 0)) return LLM_ERR_ARGUMENT;
+  if (K > 512) return LLM_ERR_UNSUPPORTED;
+  ScanArgs a;
+  a.q = q, a.q_stride = q_stride, a.k = k, a.k_stride = k_stride, a.v = v, a.v_stride = v_stride;
+  a.d = d, a.d_stride = d_stride, a.p0 = p0, a.p1 = p1, a.c = 1.f, a.q_scale = q_scale;
+  a.d2 = nullptr, a.ones = 0, a.v_cols = V;
+  a.state = state, a.state_stride = state_stride, a.out = out, a.out_stride = out_stride;
+  a.seg = seg, a.row_slot = row_slot;
+  a.single = single, a.H = H, a.G = G, a.K = K, a.V = V, a.kind = kind;
+  a.beta = beta, a.beta_stride = beta_stride, a.unit = unit ? 1 : 0, a.unit_floor = unit_floor;
+  return run_scan(a, rows, n_requests, stream);
+}
+
+// z[r][c] = exp(-exp(rate_log[c / per]) * softplus(z[r][c] + bias[c])) in place: a decay per
+// (token, head, key channel) from a projected step size, made once per token (`per` channels
+// share a rate).
+LLM_EXPORT int llm_rate_decay(float* z, const float* rate_log, const float* bias, int rows, int n, int per,
+                              cudaStream_t stream) {
+  const long long total = (long long)rows * n;
+  if (total <= 0) return 0;
+  if (per <= 0 || !rate_log) return LLM_ERR_ARGUMENT;
+  const int blocks = (int)((total + 255) / 256 < 2368 ? (total + 255) / 256 : 2368);
+  return launch_pdl(rate_decay_kernel, blocks, 256, 0, stream, z, rate_log, bias, total, n, per);
 }
 
 LLM_EXPORT int llm_bias_sigmoid_pow(float* z, const float* b, int rows, int n, float c, cudaStream_t stream) {
@@ -863,10 +1031,11 @@ LLM_EXPORT int llm_min_gru(float* z, float* u, float* g, int stride, const float
   return LLM_ERR_UNSUPPORTED;
 }
 
-LLM_EXPORT int llm_gated_group_norm(const float* o, int o_stride, const float* x, int x_stride,
-                                    const float* skip, int head, const float* g, int g_stride, const float* w,
-                                    int w_period, void* out, int out_dtype, int out_stride, int rows,
-                                    int groups, int group, float eps, int gate_first, cudaStream_t stream) {
+LLM_EXPORT int llm_gated_group_norm_act(const float* o, int o_stride, const float* x, int x_stride,
+                                        const float* skip, int head, const float* g, int g_stride, const float* w,
+                                        int w_period, void* out, int out_dtype, int out_stride, int rows,
+                                        int groups, int group, float eps, int gate_first, int gate_sigmoid,
+                                        cudaStream_t stream) {
   if (rows <= 0 || groups <= 0) return 0;
   if (group <= 0 || w_period <= 0 || (skip && (!x || head <= 0))) return LLM_ERR_ARGUMENT;
   const long long items = (long long)rows * groups;
@@ -877,7 +1046,8 @@ LLM_EXPORT int llm_gated_group_norm(const float* o, int o_stride, const float* x
                    !(((uintptr_t)o | (uintptr_t)g | (uintptr_t)w | (uintptr_t)out | (uintptr_t)x) & 15);
 #define GNV(T, TH)                                                                                             \
   return launch_pdl(gated_group_norm_vec_kernel<T, TH>, blocks, TH, 0, stream, o, o_stride, x, x_stride, skip,  \
-                    head, g, g_stride, w, w_period, (T*)out, out_stride, groups, group, eps, gate_first)
+                    head, g, g_stride, w, w_period, (T*)out, out_stride, groups, group, eps, gate_first,   \
+                    gate_sigmoid)
   if (vec && out_dtype == LLM_F32) {
     if (group <= 256) GNV(float, 32);
     if (group <= 512) GNV(float, 64);
@@ -893,7 +1063,8 @@ LLM_EXPORT int llm_gated_group_norm(const float* o, int o_stride, const float* x
 #undef GNV
 #define GN(T, TH)                                                                                          \
   return launch_pdl(gated_group_norm_kernel<T, TH>, blocks, TH, 0, stream, o, o_stride, x, x_stride, skip,  \
-                    head, g, g_stride, w, w_period, (T*)out, out_stride, groups, group, eps, gate_first)
+                    head, g, g_stride, w, w_period, (T*)out, out_stride, groups, group, eps, gate_first,   \
+                    gate_sigmoid)
   if (out_dtype == LLM_F32) {
     if (group <= 64) GN(float, 32);
     if (group <= 512) GN(float, 64);
@@ -908,4 +1079,12 @@ LLM_EXPORT int llm_gated_group_norm(const float* o, int o_stride, const float* x
   }
 #undef GN
   return LLM_ERR_UNSUPPORTED;
+}
+
+LLM_EXPORT int llm_gated_group_norm(const float* o, int o_stride, const float* x, int x_stride,
+                                    const float* skip, int head, const float* g, int g_stride, const float* w,
+                                    int w_period, void* out, int out_dtype, int out_stride, int rows,
+                                    int groups, int group, float eps, int gate_first, cudaStream_t stream) {
+  return llm_gated_group_norm_act(o, o_stride, x, x_stride, skip, head, g, g_stride, w, w_period, out, out_dtype,
+                                  out_stride, rows, groups, group, eps, gate_first, 0, stream);
 }

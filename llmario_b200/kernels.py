@@ -114,6 +114,16 @@ def _signatures():
         "llm_moe_down_rows": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, P, P],
         "llm_causal_conv_silu": [P, I, P, P, P, L, P, P, I, I, I, P, I, I, I, P],
         "llm_gated_group_norm": [P, I, P, I, P, I, P, I, P, I, P, I, I, I, I, I, F, I, P],
+        "llm_gated_group_norm_act": [P, I, P, I, P, I, P, I, P, I, P, I, I, I, I, I, F, I, I, P],
+        "llm_embed_scaled": [P, P, I, P, I, I, I, P, F, P],
+        "llm_qkv_store_mix": [P, I, P, I, P, I, P, P, P, P, P, P, I, L, P, I, P, P, I, I, I, I, I,
+                              I, I, I, F, I, I, F, I, P, I, F, P],
+        "llm_channel_gate": [P, I, P, I, I, I, I, P],
+        "llm_delta_recurrence": [P, I, P, I, P, I, P, I, P, I, P, P, F, I, F, P, L, P, I, P, P, I,
+                                 I, I, I, I, I, I, I, P],
+        "llm_rate_decay": [P, P, P, I, I, I, P],
+        "llm_moe_router_scaled": [P, I, P, P, P, I, I, I, I, I, I, I, P, P, P, F, P],
+        "llm_moe_route_scaled": [P, I, I, I, I, I, P, P, P, F, P],
     }
 
 
@@ -177,14 +187,16 @@ def _check(status: int, what: str) -> None:
 
 # ------------------------------------------------------------------------------------------
 def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
-          err_flag: torch.Tensor) -> None:
-    """out[t] = table[tokens[t]] as float32; a token outside the table sets err_flag to 1 + t."""
+          err_flag: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t] = table[tokens[t]] * scale as float32; a token outside the table sets ``err_flag``
+    (int32 [1]) to 1 + its row and gives a row of zeros."""
     _cuda(tokens, table, out, err_flag)
     assert tokens.dtype == torch.int32 and out.dtype == torch.float32
     assert table.is_contiguous() and out.is_contiguous()
-    rows, width = out.shape
-    _check(lib().llm_embed(_ptr(tokens), _ptr(table), _dt(table), _ptr(out), rows, width,
-                           table.shape[0], _ptr(err_flag), _stream()), "embed")
+    rows = tokens.numel()
+    _check(lib().llm_embed_scaled(_ptr(tokens), _ptr(table), _dt(table), _ptr(out), rows,
+                                  table.shape[1], table.shape[0], _ptr(err_flag), float(scale),
+                                  _stream()), "embed")
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
@@ -423,6 +435,16 @@ def head_gate(out: torch.Tensor, gate: torch.Tensor, num_heads: int, head_dim: i
                                head_dim, int(clear), _stream()), "head_gate")
 
 
+def channel_gate(out: torch.Tensor, gate: torch.Tensor, clear: bool = False) -> None:
+    """out[r, c] *= sigmoid(gate[r, c]); ``gate`` float32 of out's shape (a column slice of a
+    wider matrix is fine), zeroed after use with ``clear``."""
+    _cuda(out, gate)
+    assert gate.dtype == torch.float32 and gate.stride(1) == 1 and out.is_contiguous()
+    assert gate.shape == out.shape and out.dim() == 2
+    _check(lib().llm_channel_gate(_ptr(out), _dt(out), _ptr(gate), gate.stride(0), out.shape[0],
+                                  out.shape[1], int(clear), _stream()), "channel_gate")
+
+
 def segment_table(row_slot: torch.Tensor, seg: torch.Tensor) -> None:
     """seg[s, :2] = (first row, row after the last) of the step's rows whose request slot is s,
     (0, 0) for a slot without rows; seg[i, 2] = the slot of the i-th request that has rows (in
@@ -485,6 +507,50 @@ def bias_sigmoid_pow(z: torch.Tensor, bias: Optional[torch.Tensor], exponent: fl
                                       float(exponent), _stream()), "bias_sigmoid_pow")
 
 
+def rate_decay(z: torch.Tensor, rate_log: torch.Tensor, bias: Optional[torch.Tensor],
+               per: int) -> None:
+    """z = exp(-exp(rate_log[c // per]) * softplus(z + bias[c])) in place for column c (float32
+    [rows, n], contiguous): the decay of a recurrence from a projected step size, ``per``
+    neighbouring columns sharing a rate."""
+    _cuda(z, rate_log, bias)
+    assert z.dtype == torch.float32 and z.is_contiguous() and z.dim() == 2
+    n = z.shape[1]
+    assert rate_log.dtype == torch.float32 and rate_log.numel() * per == n
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == n)
+    _check(lib().llm_rate_decay(_ptr(z), _ptr(rate_log), _ptr(bias), z.shape[0], n, int(per),
+                                _stream()), "rate_decay")
+
+
+def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d: torch.Tensor,
+                     beta: torch.Tensor, state: torch.Tensor, out: torch.Tensor,
+                     row_slot: torch.Tensor, seg: Optional[torch.Tensor], heads: int, groups: int,
+                     key_dim: int, value_dim: int, kind: int, q_scale: float = 1.0,
+                     unit_floor: Optional[float] = None,
+                     rate_log: Optional[torch.Tensor] = None,
+                     step_bias: Optional[torch.Tensor] = None, n_requests: int = 0) -> None:
+    """The gated delta rule per request and head over the rows of the step in order:
+    ``S <- diag(a_t) S``, ``u = sigmoid(beta_t) (v_t - S^T k_t)``, ``S <- S + k_t u^T``,
+    ``o_t = S^T q_t``.  Tensors, state and ``seg`` as in :func:`linear_recurrence`; ``beta``
+    float32 [rows, heads] (a column slice is fine).  ``kind`` DECAY_VECTOR: ``d``
+    [rows, heads * key_dim] is the decay; DECAY_RATE_STEP: ``d`` [rows, heads] and
+    ``a = exp(-exp(rate_log[h]) softplus(d + step_bias[h]))`` for every key channel of head h.
+    ``unit_floor`` (not None): q and k of every head are first divided by
+    ``sqrt(sum of squares + unit_floor)``; q is then multiplied by ``q_scale``."""
+    _cuda(q, k, v, d, beta, state, out, row_slot, seg, rate_log, step_bias)
+    for t in (q, k, v, d, beta, state, out):
+        assert t.dtype == torch.float32 and t.stride(-1) == 1
+    rows = out.shape[0]
+    assert state.dim() == 2 and state.shape[1] >= heads * value_dim * key_dim
+    assert kind in (DECAY_VECTOR, DECAY_RATE_STEP)
+    _check(lib().llm_delta_recurrence(
+        _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(d), d.stride(0),
+        _ptr(beta), beta.stride(0), _ptr(rate_log), _ptr(step_bias), float(q_scale),
+        int(unit_floor is not None), float(unit_floor or 0.0), _ptr(state), state.stride(0),
+        _ptr(out), out.stride(0), _ptr(seg), _ptr(row_slot), rows, int(n_requests),
+        int(seg is None), heads, groups, key_dim, value_dim, kind, _stream()),
+        f"delta_recurrence (key_dim {key_dim})")
+
+
 def causal_conv_silu(src: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
                      history: torch.Tensor, out: torch.Tensor, row_slot: torch.Tensor,
                      seg: Optional[torch.Tensor], activation: bool = True) -> None:
@@ -511,22 +577,25 @@ def causal_conv_silu(src: torch.Tensor, weight: torch.Tensor, bias: Optional[tor
 def gated_group_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor,
                      out: torch.Tensor, group: int, eps: float, gate_first: bool,
                      skip: Optional[torch.Tensor] = None, skip_input: Optional[torch.Tensor] = None,
-                     head: int = 0) -> None:
+                     head: int = 0, gate_activation: str = "silu") -> None:
     """The recurrence's output through its gate and a norm over groups of ``group`` channels:
     ``y = o (+ skip[ch // head] * skip_input)``; with ``gate_first``
     ``out = unit(y * silu(gate)) * weight`` else ``out = unit(y) * weight * silu(gate)``, where
     unit divides each group by its root mean square.  ``weight`` is indexed by the channel
-    modulo its length.  o, gate, skip_input float32 [rows, channels] (column slices are fine)."""
+    modulo its length.  o, gate, skip_input float32 [rows, channels] (column slices are fine).
+    ``gate_activation="sigmoid"``: ``sigmoid(gate)`` stands where ``silu(gate)`` does."""
     _cuda(o, gate, weight, out, skip, skip_input)
+    if gate_activation not in ("silu", "sigmoid"):
+        raise KernelError(f"the gate of a group norm is silu or sigmoid, not '{gate_activation}'")
     rows, channels = out.shape
     assert o.dtype == gate.dtype == weight.dtype == torch.float32 and channels % group == 0
     assert o.stride(1) == 1 and gate.stride(1) == 1 and out.stride(1) == 1
     assert (skip is None) == (skip_input is None)
-    _check(lib().llm_gated_group_norm(
+    _check(lib().llm_gated_group_norm_act(
         _ptr(o), o.stride(0), _ptr(skip_input), skip_input.stride(0) if skip is not None else 0,
         _ptr(skip), head, _ptr(gate), gate.stride(0), _ptr(weight), weight.numel(), _ptr(out),
         _dt(out), out.stride(0), rows, channels // group, group, float(eps), int(gate_first),
-        _stream()), "gated_group_norm")
+        int(gate_activation == "sigmoid"), _stream()), "gated_group_norm")
 
 
 def min_gru(z: torch.Tensor, u: torch.Tensor, g: torch.Tensor, z_bias: Optional[torch.Tensor],
@@ -561,15 +630,25 @@ def qkv_store(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tens
               q_out: torch.Tensor, view, row_slot: torch.Tensor, row_pos: torch.Tensor,
               num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, head_dim: int,
               norm: int, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
-              eps: float, rot_dim: int = 0, cos_sin: Optional[torch.Tensor] = None) -> None:
+              eps: float, rot_dim: int = 0, cos_sin: Optional[torch.Tensor] = None,
+              q_temp: Optional[Tuple[float, int]] = None,
+              blend: Optional[Tuple[torch.Tensor, float]] = None) -> None:
     """Norm, rotation and stores for the rows of a step.  q float32 [rows, heads * key_dim],
     k [rows, kv_heads * key_dim], v [rows, kv_heads * value_dim] (column slices are fine; k and
     v None: only the queries).  ``norm``: NORM_NONE, NORM_PER_HEAD (weights [key_dim], shared by
     the heads) or NORM_WHOLE_ROW (weights of the whole q and k rows).  ``rot_dim`` > 0: the
     pairs (2i, 2i + 1) of every q and k head are turned by ``cos_sin`` (float32
     [rows, rot_dim / 2, 2]).  q goes to ``q_out`` [rows, heads * head_dim], k and v into the
-    pages of ``view``; ``head_dim`` >= both sizes is the cache's row, padded with zeros."""
+    pages of ``view``; ``head_dim`` >= both sizes is the cache's row, padded with zeros.
+    ``q_temp = (coef, every)``: the queries of position p are multiplied by
+    ``1 + coef ln(floor((p + 1) / every) + 1)``.  ``blend = (v0, lam)``: what is stored as the
+    value is ``(1 - lam) v + lam v0`` with v0 float32 of v's shape (a column slice is fine)."""
     _cuda(q, k, v, q_out, q_weight, k_weight, cos_sin, row_slot, row_pos)
+    coef, every = q_temp if q_temp is not None else (0.0, 0)
+    v0, lam = blend if blend is not None and k is not None else (None, 0.0)
+    if v0 is not None:
+        _cuda(v0)
+        assert v0.dtype == torch.float32 and v0.stride(1) == 1 and v0.shape == v.shape
     rows = q.shape[0]
     has_kv = k is not None
     for t in (q, k, v):
@@ -583,13 +662,14 @@ def qkv_store(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tens
         if norm != NORM_NONE and w is not None:
             assert w.dtype == torch.float32 and w.is_contiguous()
             assert w.numel() == (key_dim if norm == NORM_PER_HEAD else n * key_dim)
-    _check(lib().llm_qkv_store(
+    _check(lib().llm_qkv_store_mix(
         _ptr(q), q.stride(0), _ptr(k), k.stride(0) if has_kv else 0, _ptr(v),
         v.stride(0) if has_kv else 0, _ptr(q_weight), _ptr(k_weight), _ptr(cos_sin), _ptr(q_out),
         _ptr(view.k) if has_kv else None, _ptr(view.v) if has_kv else None, _dt(q_out),
         view.page_stride, _ptr(view.block_table), view.block_table.stride(0), _ptr(row_slot),
         _ptr(row_pos), rows, num_heads, num_kv_heads, key_dim, value_dim, head_dim, rot_dim, norm,
-        float(eps), view.page_size, int(has_kv), _stream()), "qkv_store")
+        float(eps), view.page_size, int(has_kv), float(coef), int(every), _ptr(v0),
+        v0.stride(0) if v0 is not None else 0, float(lam), _stream()), "qkv_store")
 
 
 def pool_blocks(view, pooled_view, row_slot: torch.Tensor, row_pos: torch.Tensor, rows: int,
@@ -1322,42 +1402,48 @@ def head_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
                                        out.stride(1), _stream()), "head_linear")
 
 
-ROUTE_SOFTMAX_CHOSEN, ROUTE_SOFTMAX_ALL = 0, 1
+ROUTE_SOFTMAX_CHOSEN, ROUTE_SOFTMAX_ALL, ROUTE_SOFTMAX_ALL_RENORMED = 0, 1, 2
+ROUTE_MODES = {"softmax_chosen": ROUTE_SOFTMAX_CHOSEN, "softmax_all": ROUTE_SOFTMAX_ALL,
+               "softmax_all_renormed": ROUTE_SOFTMAX_ALL_RENORMED}
 
 
 def _route_mode(scores: str, correction: Optional[torch.Tensor], experts: int) -> int:
-    if scores not in ("softmax_chosen", "softmax_all"):
-        raise KernelError(f"router scores '{scores}' (softmax_chosen or softmax_all)")
+    if scores not in ROUTE_MODES:
+        raise KernelError(f"router scores '{scores}' ({', '.join(ROUTE_MODES)})")
     if correction is not None:
-        assert scores == "softmax_all" and correction.dtype == torch.float32
+        assert scores != "softmax_chosen" and correction.dtype == torch.float32
         assert correction.is_contiguous() and correction.numel() == experts
-    return ROUTE_SOFTMAX_ALL if scores == "softmax_all" else ROUTE_SOFTMAX_CHOSEN
+    return ROUTE_MODES[scores]
 
 
 def moe_route(z: torch.Tensor, experts: int, top: int, ids: torch.Tensor, wts: torch.Tensor,
-              scores: str = "softmax_chosen", correction: Optional[torch.Tensor] = None) -> None:
+              scores: str = "softmax_chosen", correction: Optional[torch.Tensor] = None,
+              weight_scale: float = 1.0) -> None:
     """Per row the ``top`` largest of the first ``experts`` logits of z (float32, a column slice
     is fine) into ``ids`` (int32 [rows, top]) and the softmax over the chosen into ``wts``.
     ``scores="softmax_all"``: the scores are the softmax over all ``experts`` logits, the choice
     goes by score + ``correction`` (float32 [experts], optional), and a chosen expert's weight is
-    its score, not renormalised."""
+    its score, not renormalised.  ``"softmax_all_renormed"``: the same choice; the weights are the
+    chosen scores over their sum (+ 1e-20), times ``weight_scale``."""
     _cuda(z, ids, wts, correction)
     mode = _route_mode(scores, correction, experts)
     rows = z.shape[0]
     assert z.dtype == torch.float32 and z.stride(1) == 1 and z.shape[1] >= experts
     assert ids.dtype == torch.int32 and ids.is_contiguous() and ids.shape == (rows, top)
     assert wts.dtype == torch.float32 and wts.is_contiguous() and wts.shape == (rows, top)
-    _check(lib().llm_moe_route(_ptr(z), z.stride(0), rows, experts, top, mode, _ptr(correction),
-                               _ptr(ids), _ptr(wts), _stream()), "moe_route")
+    _check(lib().llm_moe_route_scaled(_ptr(z), z.stride(0), rows, experts, top, mode,
+                                      _ptr(correction), _ptr(ids), _ptr(wts),
+                                      float(weight_scale), _stream()), "moe_route")
 
 
 def moe_router(h: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], experts: int,
                top: int, z: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor,
-               scores: str = "softmax_chosen", correction: Optional[torch.Tensor] = None) -> None:
+               scores: str = "softmax_chosen", correction: Optional[torch.Tensor] = None,
+               weight_scale: float = 1.0) -> None:
     """Router logits ``z = h w^T + bias`` (w float32 [n_out, width], sums in 32-bit) and, over
     the first ``experts`` of them, the ``top`` largest per row into ``ids`` with the softmax over
-    the chosen into ``wts``: the product and :func:`moe_route` in one launch (``scores`` and
-    ``correction`` as there)."""
+    the chosen into ``wts``: the product and :func:`moe_route` in one launch (``scores``,
+    ``correction`` and ``weight_scale`` as there)."""
     _cuda(h, w, bias, z, ids, wts, correction)
     mode = _route_mode(scores, correction, experts)
     rows, width = h.shape
@@ -1367,9 +1453,10 @@ def moe_router(h: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], e
     assert z.stride(1) == 1 and (bias is None or (bias.dtype == torch.float32 and bias.numel() == n_out))
     assert ids.dtype == torch.int32 and ids.is_contiguous() and ids.shape == (rows, top)
     assert wts.dtype == torch.float32 and wts.is_contiguous() and wts.shape == (rows, top)
-    _check(lib().llm_moe_router(_ptr(h), _dt(h), _ptr(w), _ptr(bias), _ptr(z), z.stride(0), rows,
-                                width, experts, n_out, top, mode, _ptr(correction), _ptr(ids),
-                                _ptr(wts), _stream()),
+    _check(lib().llm_moe_router_scaled(_ptr(h), _dt(h), _ptr(w), _ptr(bias), _ptr(z),
+                                       z.stride(0), rows, width, experts, n_out, top, mode,
+                                       _ptr(correction), _ptr(ids), _ptr(wts),
+                                       float(weight_scale), _stream()),
            "moe_router")
 
 
@@ -1377,17 +1464,20 @@ def moe_gate_up_rows(h: torch.Tensor, gate_up: torch.Tensor, ids: torch.Tensor,
                      act: torch.Tensor, activation: str = "silu", limit: float = 0.0) -> None:
     """act[r, k] = silu(Wg_e h_r) * (Wu_e h_r), e = ids[r, k]; gate_up [E, 2 ff, width].  With
     ``activation="clamped_swish"`` the gated form of that name (see :func:`gated_act`).  A pair
-    whose expert is not one of the E with matrices is left out."""
+    whose expert is not one of the E with matrices is left out.  ``activation="relu_squared"``:
+    experts without a gate, ``gate_up`` [E, ff, width] holds their up matrices and
+    act[r, k] = max(Wu_e h_r, 0)^2."""
     _cuda(h, gate_up, ids, act)
-    if activation not in ("silu", "clamped_swish"):
+    if activation not in ("silu", "clamped_swish", "relu_squared"):
         raise KernelError(f"routed experts have no activation '{activation}'")
     rows, width = h.shape
     top = ids.shape[1]
-    ff = gate_up.shape[1] // 2
+    ff = gate_up.shape[1] if activation == "relu_squared" else gate_up.shape[1] // 2
     assert h.is_contiguous() and gate_up.is_contiguous() and act.is_contiguous()
     assert h.dtype == gate_up.dtype == act.dtype and act.shape == (rows, top, ff)
     _check(lib().llm_moe_gate_up_rows(_ptr(h), _ptr(gate_up), _ptr(ids), _ptr(act), _dt(h), rows,
-                                      width, ff, top, gate_up.shape[0], ACTIVATIONS[activation],
+                                      width, ff, top, gate_up.shape[0],
+                                      {**ACTIVATIONS, **PLAIN_ACTIVATIONS}[activation],
                                       float(limit), _stream()), "moe_gate_up_rows")
 
 

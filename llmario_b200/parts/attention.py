@@ -24,9 +24,20 @@ Options that are data of the part's spec (each absent by default):
   reads the cache of an earlier call, with its own queries and mask.  The layer whose cache is
   read says with ``cache_window`` / ``cache_keep_first`` what its readers need it to keep.
 
-The last four run through the store kernel of ``csrc/qkv_store.cu`` (which also turns adjacent
-pairs itself) and the attention call with the matching arguments; a layer without them runs as
-before.
+* ``q_temp = {"coef": c, "every": n}``: the queries of position p are multiplied by
+  ``1 + c ln(floor((p + 1) / n) + 1)``;
+* ``value_blend = {"group": name, "source": bool}`` with the tensor role ``blend`` (one number
+  lambda) on the layers that are no source: such a layer stores and attends to
+  ``(1 - lambda) v + lambda v0`` where v0 are the values that the group's source layer projected
+  for the same tokens (the source stores its own values unchanged; its ``blend`` is not read);
+* tensor role ``gate`` of shape [heads * value_dim, hidden]: a sigmoid gate per output channel
+  in the place of one per head.
+
+These run through the store kernel of ``csrc/qkv_store.cu`` (which also turns adjacent
+pairs itself; the pairs (i, i + rot_dim/2) of ``rope_neox`` are brought side by side by
+ordering the rows of the q and k projections accordingly) and the attention call with the
+matching arguments; a layer without them runs as before.  There the biases (roles ``q_bias``,
+``k_bias``, ``v_bias``, ``o_bias``) and the gate per head are taken as well.
 """
 from __future__ import annotations
 
@@ -70,9 +81,25 @@ class Attention:
                               f"{self.num_heads} heads")
         if self.keep_first and not self.window:
             raise ConfigError("attention: keep_first needs a window")
+        self.fusable = False      # (see in_proj)
+        self.q_temp = None
+        if spec.get("q_temp") is not None:
+            self.q_temp = (float(spec["q_temp"]["coef"]), int(spec["q_temp"]["every"]))
+            if self.q_temp[1] < 1:
+                raise ConfigError(f"attention: q_temp every {self.q_temp[1]} must be positive")
+        self.blend_group = self.blend_source = self.blend = None
+        if spec.get("value_blend") is not None:
+            self.blend_group = str(spec["value_blend"]["group"])
+            self.blend_source = bool(spec["value_blend"].get("source"))
+            if not self.blend_source:
+                self.blend = float(tensor_of(spec, "blend", weights).to(torch.float32).reshape(()))
+        gate_entry = spec["tensors"].get("gate")
+        self.gate_per_channel = gate_entry is not None and \
+            int(gate_entry[1][0]) == self.num_heads * self.value_dim != self.num_heads
         # what the store kernel of several forms serves (see the module's text)
         self.general = bool(self.keep_first or self.sink is not None or self.shared_kv
-                            or self.value_dim != self.head_dim)
+                            or self.value_dim != self.head_dim or self.q_temp is not None
+                            or self.blend_group is not None or self.gate_per_channel)
         if self.general:
             self._init_general(spec, weights, dtype, device)
             return
@@ -137,10 +164,12 @@ class Attention:
         self.o_proj = Linear(tensor_of(spec, "o", weights), b["o"])
 
     def _init_general(self, spec: PartSpec, weights, dtype, device) -> None:
-        if self.chunk is not None or self.values_are_keys or spec["tensors"].get("gate"):
-            raise ConfigError("attention: kept first keys, a sink, shared keys and values or a "
-                              "value size of its own do not combine with a chunked mask, "
-                              "values that are keys or a gate per head")
+        if self.chunk is not None or self.values_are_keys:
+            raise ConfigError("attention: kept first keys, a sink, shared keys and values, a "
+                              "value size of its own, a query temperature or blended values do "
+                              "not combine with a chunked mask or values that are keys")
+        if self.blend_group is not None and self.shared_kv:
+            raise ConfigError("attention: a layer without values of its own blends none")
         d, dv = self.head_dim, self.value_dim
         self.cache_dim = max(d, dv)
         refusal = kernels.attention_refusal(self.num_heads, self.num_kv_heads, self.cache_dim)
@@ -148,9 +177,6 @@ class Attention:
             raise ConfigError(f"attention: {refusal}")
         self.position = (build_part("position", spec["position"], weights, dtype, device)
                          if spec.get("position") is not None else None)
-        if self.position is not None and not hasattr(self.position, "head_permutation"):
-            raise ConfigError("attention: with these options the rotation is that of adjacent "
-                              "pairs (rope_normal)")
         qn, kn = spec.get("q_norm"), spec.get("k_norm")
         self.q_norm = build_part("norm", qn, weights, dtype, device) if qn is not None else None
         self.k_norm = build_part("norm", kn, weights, dtype, device) if kn is not None else None
@@ -161,16 +187,71 @@ class Attention:
             raise ValueError("q_norm and k_norm come together")
         self.q_width = self.num_heads * d
         self.k_cols, self.v_cols = self.num_kv_heads * d, self.num_kv_heads * dv
-        mats = [tensor_of(spec, "q", weights)]
-        if not self.shared_kv:
-            mats += [tensor_of(spec, "k", weights), tensor_of(spec, "v", weights)]
+        roles = ["q"] + ([] if self.shared_kv else ["k", "v"])
+        w = {r: tensor_of(spec, r, weights) for r in roles}
+        b = {r: optional_tensor_of(spec, r + "_bias", weights) for r in roles + ["o"]}
+        if self.position is not None and not hasattr(self.position, "head_permutation"):
+            # The store kernel turns the pairs (2i, 2i + 1); this encoding turns (i, i + rot/2).
+            # A head's scores do not change when queries and keys are reordered alike, so the
+            # rows of the q and k projections (with bias and norm gain) are ordered once here
+            # such that the members of every pair stand side by side.
+            _, rot, _ = self.position.rotary_tables()
+            order = [j for i in range(rot // 2) for j in (i, i + rot // 2)] + list(range(rot, d))
+            perm = torch.tensor(order, dtype=torch.long, device=w["q"].device)
+            for r, heads in (("q", self.num_heads), ("k", self.num_kv_heads)):
+                if r not in w:
+                    continue
+                w[r] = w[r].view(heads, d, -1)[:, perm].reshape(w[r].shape)
+                if b[r] is not None:
+                    b[r] = b[r].view(heads, d)[:, perm].reshape(-1)
+            for norm in (self.q_norm, self.k_norm):
+                if norm is not None:
+                    norm.weight = norm.weight[perm.to(norm.weight.device)].contiguous()
+        mats, biases = [w[r] for r in roles], [b[r] for r in roles]
+        self.gate_col = None
+        gate = optional_tensor_of(spec, "gate", weights)
+        if gate is not None:
+            self.gate_cols = self.num_heads * (dv if self.gate_per_channel else 1)
+            if tuple(gate.shape) != (self.gate_cols, self.hidden):
+                raise ConfigError(f"attention: a gate of {list(gate.shape)} for "
+                                  f"{self.num_heads} heads of {dv} value channels")
+            # (the gates start a column range of whole 16-byte units)
+            n_rows = sum(m.shape[0] for m in mats)
+            if n_rows % 4:
+                mats.append(torch.zeros(4 - n_rows % 4, self.hidden, dtype=mats[0].dtype,
+                                        device=mats[0].device))
+                biases.append(None)
+            self.gate_col = sum(m.shape[0] for m in mats)
+            mats.append(gate)
+            biases.append(None)
         n_rows = sum(m.shape[0] for m in mats)
         if n_rows % 16:
             mats.append(torch.zeros(16 - n_rows % 16, self.hidden, dtype=mats[0].dtype,
                                     device=mats[0].device))
-        self.qkv_proj = Linear.stacked(mats)
+            biases.append(None)
+        self.qkv_proj = Linear.stacked(mats, biases)
         # (attention writes value_dim channels per head, so the projection is as stored)
-        self.o_proj = Linear(tensor_of(spec, "o", weights))
+        self.o_proj = Linear(tensor_of(spec, "o", weights), b["o"])
+        self.fusable = self.qkv_proj.bias is None and self.blend_group is None
+
+    @property
+    def in_proj(self) -> Linear:
+        """The one product of the mixer's input, offered to a part that runs this mixer beside
+        another one on the same input and wants a single product for both (it then calls
+        :meth:`run` with this mixer's columns of the result).  Only a layer whose projections
+        need nothing else (no bias, no buffer that outlives the layer) offers it."""
+        if not self.fusable:
+            raise AttributeError("in_proj")
+        return self.qkv_proj
+
+    @in_proj.setter
+    def in_proj(self, proj: Linear) -> None:
+        self.qkv_proj = proj
+
+    def run(self, ctx: StepContext, call: BoundCall, proj: torch.Tensor, x: torch.Tensor,
+            accumulate: bool) -> None:
+        """From the projections ``proj`` (float32, the columns of :attr:`in_proj`) to the output."""
+        self._run_general(ctx, call, proj, x, accumulate)
 
     def cache_need(self):
         # (no query ever looks back further than a chunk is long: pages behind that go back)
@@ -185,6 +266,15 @@ class Attention:
 
     def _forward_general(self, ctx: StepContext, call: BoundCall, h: torch.Tensor,
                          x: torch.Tensor, accumulate: bool) -> None:
+        # (the values that other layers of a group blend in stay where their layer projected
+        # them until the step ends)
+        name = "attn.gproj" if not self.blend_source else "attn.gproj." + self.blend_group
+        proj = ctx.buffer(name, (ctx.rows, self.qkv_proj.out_features), torch.float32)
+        self.qkv_proj(h, proj)
+        self._run_general(ctx, call, proj, x, accumulate)
+
+    def _run_general(self, ctx: StepContext, call: BoundCall, proj: torch.Tensor,
+                     x: torch.Tensor, accumulate: bool) -> None:
         rows, d, dv, hd = ctx.rows, self.head_dim, self.value_dim, self.cache_dim
         view = ctx.cache.view(call.cache_entry)
         if view is None:
@@ -193,8 +283,19 @@ class Attention:
             raise RuntimeError(f"run-order entry {call.index}: a layer without key and value "
                                "projections must read another call's cache")
         writes = call.writes_cache
-        proj = ctx.buffer("attn.gproj", (rows, self.qkv_proj.out_features), torch.float32)
-        self.qkv_proj(h, proj)
+        a, c = self.q_width + self.k_cols, self.q_width + self.k_cols + self.v_cols
+        blend = None
+        if self.blend_group is not None and writes:
+            key = ("attention.values", self.blend_group)
+            if self.blend_source:
+                ctx.shared[key] = proj[:, a:c]
+            else:
+                first = ctx.shared.get(key)
+                if first is None or first.shape != (rows, self.v_cols):
+                    raise RuntimeError(f"run-order entry {call.index}: the values of group "
+                                       f"'{self.blend_group}' were not made in this step by a "
+                                       "layer of the same value size")
+                blend = (first, self.blend)
         cos_sin, rot = None, 0
         if self.position is not None:
             _, rot, _ = self.position.rotary_tables()
@@ -209,11 +310,18 @@ class Attention:
             q, view, ctx.row_slot, ctx.row_pos, self.num_heads, self.num_kv_heads, d, dv, hd,
             norm, self.q_norm.weight if self.q_norm is not None else None,
             self.k_norm.weight if self.k_norm is not None and writes else None,
-            self.q_norm.eps if self.q_norm is not None else 0.0, rot, cos_sin)
+            self.q_norm.eps if self.q_norm is not None else 0.0, rot, cos_sin,
+            q_temp=self.q_temp, blend=blend)
         out = ctx.buffer("attn.out", (rows, self.num_heads * dv))
         driver.attention(ctx, q, out, view, self.num_heads, self.num_kv_heads, hd, self.scale,
                          self.mask, sink=self.sink, value_dim=dv if dv != hd else None,
                          keep_first=self.keep_first)
+        if self.gate_col is not None:
+            gate = proj[:, self.gate_col:self.gate_col + self.gate_cols]
+            if self.gate_per_channel:
+                kernels.channel_gate(out, gate)
+            else:
+                kernels.head_gate(out, gate, self.num_heads, dv)
         self.o_proj(out, x, accumulate=accumulate)
 
     def forward(self, ctx: StepContext, call: BoundCall, h: torch.Tensor, x: torch.Tensor,

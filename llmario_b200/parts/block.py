@@ -1,6 +1,7 @@
 """Pre-norm residual arrangement: ``x += mixer(norm(x)); x += feed_forward(norm(x))``
-(crates/engine/model/src/forward.rs:356-362), and the arrangement with the norm on the
-sublayer's output.  The residual stream ``x`` is 32-bit in every mode; the parts add into it."""
+(crates/engine/model/src/forward.rs:356-362), the arrangement with the norm on the
+sublayer's output, the one over several residual streams, and the one whose two sublayers read
+the same normed input (``x += mixer(norm(x)) + feed_forward(norm(x))``).  The residual stream ``x`` is 32-bit in every mode; the parts add into it."""
 from __future__ import annotations
 
 from typing import Dict
@@ -218,6 +219,36 @@ class HyperConnectionBlock:
         ctx.shared["streams.pending"] = write
 
 
+class SharedNormResidualBlock:
+    """One norm, both sublayers read its output: ``h = norm(x); x += mixer(h) + feed_forward(h)``.
+    The sublayers add into the 32-bit stream one after the other; a feed-forward of kind ``none``
+    leaves the mixer alone."""
+
+    def __init__(self, spec: PartSpec, layer: LayerSpec, weights: Dict[str, torch.Tensor],
+                 dtype, device):
+        self.norm = build_part("norm", spec["norm"], weights, dtype, device)
+        self.mixer = build_part("mixer", layer.mixer, weights, dtype, device)
+        self.feed_forward = build_part("feed_forward", layer.feed_forward, weights, dtype,
+                                       device)
+
+    def cache_needs(self):
+        return cache_needs_of(self.mixer)
+
+    def streamed_weights(self):
+        return streamed_weights_of(self.mixer) + streamed_weights_of(self.feed_forward)
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(graph_safe(p) for p in (self.norm, self.mixer, self.feed_forward))
+
+    def forward(self, ctx: StepContext, call: BoundCall, x: torch.Tensor) -> None:
+        h = ctx.buffer("block.h", x.shape)
+        self.norm.apply(ctx, x, h)
+        self.mixer.forward(ctx, call.for_need(0) if call.cache_entries else call, h, x)
+        self.feed_forward.forward(ctx, h, x)
+
+
 register_part("block", "pre_norm_residual", PreNormResidualBlock, replace=True)
+register_part("block", "shared_norm_residual", SharedNormResidualBlock, replace=True)
 register_part("block", "hyper_connection", HyperConnectionBlock, replace=True)
 register_part("block", "output_norm_residual", OutputNormResidualBlock, replace=True)

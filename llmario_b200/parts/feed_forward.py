@@ -10,7 +10,10 @@ per-token scalar weight, the sigmoid of one more projection of the input.  Optio
 experts: ``scores: "softmax_all"`` (the scores are the softmax over all router outputs, the choice
 goes by score plus the tensor ``correction``, and a chosen expert's weight is its score, not
 renormalised); ``identity`` (the last so many router outputs are experts without matrices whose
-output is the input itself); ``activation: "clamped_swish"`` with ``limit``.
+output is the input itself); ``activation: "clamped_swish"`` with ``limit``;
+``scores: "softmax_all_renormed"`` (as ``softmax_all``, but the weights are the chosen scores over
+their sum, times ``weight_scale``); ``activation: "relu_squared"`` (experts without a gate,
+``W_down max(W_up h, 0)^2``: there are no ``gate<e>`` tensors).
 
 And a feed-forward without a gate (kind ``dense``): ``y = W_down act(W_up h)``."""
 from __future__ import annotations
@@ -168,10 +171,15 @@ class RoutedExperts:
         self.scores = spec.get("scores", "softmax_chosen")
         self.activation = spec.get("activation", "silu")
         self.limit = float(spec.get("limit") or 0.0)
-        if self.scores not in ("softmax_chosen", "softmax_all"):
+        self.weight_scale = float(spec.get("weight_scale") or 1.0)
+        self.gated = self.activation != "relu_squared"
+        if self.scores not in kernels.ROUTE_MODES:
             raise ConfigError(f"routed experts: scores '{self.scores}'")
-        if self.activation not in ("silu", "clamped_swish"):
+        if self.activation not in ("silu", "clamped_swish", "relu_squared"):
             raise ConfigError(f"routed experts: activation '{self.activation}'")
+        if self.weight_scale != 1.0 and self.scores != "softmax_all_renormed":
+            raise ConfigError("routed experts: a scale of the weights needs scores "
+                              "'softmax_all_renormed'")
         if not 1 <= self.top <= min(self.routed, 16):
             raise ConfigError(f"routed experts: top {self.top} of {self.routed} (at most 16)")
         router = tensor_of(spec, "router", weights).to(torch.float32)
@@ -181,9 +189,9 @@ class RoutedExperts:
         corr = optional_tensor_of(spec, "correction", weights)
         self.correction = None if corr is None else \
             corr.to(device=router.device, dtype=torch.float32).contiguous()
-        if self.correction is not None and self.scores != "softmax_all":
-            raise ConfigError("routed experts: a correction of the choice needs scores "
-                              "'softmax_all'")
+        if self.correction is not None and self.scores == "softmax_chosen":
+            raise ConfigError("routed experts: a correction of the choice needs scores over "
+                              "all router outputs")
         bias = optional_tensor_of(spec, "router_bias", weights)
         bias = torch.zeros(self.routed, device=router.device) if bias is None \
             else bias.to(torch.float32)
@@ -197,12 +205,17 @@ class RoutedExperts:
             bias = torch.cat([bias, torch.zeros(1, device=bias.device)])
         # the router (and the shared expert's gate as its last row) stays 32-bit
         self.router = Linear(router.contiguous(), bias)
-        self.gate_up = torch.stack([torch.cat([tensor_of(spec, f"gate{e}", weights),
-                                               tensor_of(spec, f"up{e}", weights)])
-                                    for e in range(E)]).contiguous()           # [E, 2 ff, W]
+        if self.gated:
+            self.gate_up = torch.stack([torch.cat([tensor_of(spec, f"gate{e}", weights),
+                                                   tensor_of(spec, f"up{e}", weights)])
+                                        for e in range(E)]).contiguous()           # [E, 2 ff, W]
+        else:       # (the name stays: without a gate it holds the up matrices alone, [E, ff, W])
+            self.gate_up = torch.stack([tensor_of(spec, f"up{e}", weights)
+                                        for e in range(E)]).contiguous()
         self.down = torch.stack([tensor_of(spec, f"down{e}", weights)
                                  for e in range(E)]).contiguous()              # [E, W, ff]
-        if tuple(self.gate_up.shape) != (E, 2 * ff, W) or tuple(self.down.shape) != (E, W, ff):
+        if tuple(self.gate_up.shape) != (E, (2 if self.gated else 1) * ff, W) or \
+                tuple(self.down.shape) != (E, W, ff):
             raise ConfigError("routed experts: the experts' matrices do not have the spec's sizes")
 
     def streamed_weights(self):
@@ -219,10 +232,11 @@ class RoutedExperts:
         wts = ctx.buffer("moe.weights", (rows, top), torch.float32)
         if (self.hidden + self.router.out_features) * 4 <= 200 * 1024:
             kernels.moe_router(h, self.router.weight, self.router.bias, R, top, z, ids, wts,
-                               self.scores, self.correction)
+                               self.scores, self.correction, self.weight_scale)
         else:           # a row too wide to stage: the product, then the choice
             self.router(h, z)
-            kernels.moe_route(z, R, top, ids, wts, self.scores, self.correction)
+            kernels.moe_route(z, R, top, ids, wts, self.scores, self.correction,
+                              self.weight_scale)
         ident = h if self.identity else None
         shared = gate = None
         kept_zero = rows <= kernels.SPLIT_K_MAX_ROWS
@@ -246,6 +260,10 @@ class RoutedExperts:
             act = ctx.buffer("moe.act", (tiles * bn, self.ff))
             if self.activation == "silu":
                 kernels.gemm_grouped(xp, self.gate_up, act, tile_group, bn, gated=True)
+            elif not self.gated:
+                u = ctx.buffer("moe.up", (tiles * bn, self.ff), torch.float32)
+                kernels.gemm_grouped(xp, self.gate_up, u, tile_group, bn, gated=False)
+                kernels.act_rows(u, act, self.activation)
             else:       # the product as it is, then the activation over the padded buffer
                 gu = ctx.buffer("moe.gate_up", (tiles * bn, 2 * self.ff), torch.float32)
                 kernels.gemm_grouped(xp, self.gate_up, gu, tile_group, bn, gated=False)

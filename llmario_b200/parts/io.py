@@ -1,4 +1,5 @@
-"""Token embedding (row gather, no scaling: crates/engine/model/src/forward.rs:343-349) and the
+"""Token embedding (row gather; no scaling, crates/engine/model/src/forward.rs:343-349, unless
+the spec gives a ``scale`` that multiplies every row as it enters the residual stream) and the
 output head (``logits = H h`` with ``H`` the output matrix or, when tied, the embedding table:
 forward.rs:303-316).  Options of the head: ``scale`` multiplies the logits, ``soft_cap`` then
 bounds them smoothly (``cap * tanh(z / cap)``)."""
@@ -20,12 +21,13 @@ class TokenEmbedding:
     def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
         self.table = tensor_of(spec, "table", weights)
         self.vocab, self.hidden = self.table.shape
+        self.scale = float(spec.get("scale") or 1.0)
         # word 1 of the library's status words: read by the host with every step's tokens
         self.err = kernels.status_words(device)[1:2] if torch.device(device).type == "cuda" \
             else torch.zeros(1, dtype=torch.int32, device=device)
 
     def forward(self, ctx: StepContext, tokens: torch.Tensor, x: torch.Tensor) -> None:
-        kernels.embed(tokens, self.table, x, self.err)
+        kernels.embed(tokens, self.table, x, self.err, self.scale)
 
 
 class LinearHead:

@@ -175,8 +175,7 @@ class ParallelMixers:
         return cache_needs_of(self.left) + cache_needs_of(self.right)
 
     def streamed_weights(self):
-        if self.in_proj is not None:
-            return [self.in_proj.weight, self.left.o_proj.weight, self.right.o_proj.weight]
+        # (with one product for both, the halves' own are its rows: views of one tensor)
         return streamed_weights_of(self.left) + streamed_weights_of(self.right)
 
     @staticmethod

@@ -24,8 +24,18 @@
   ``c = u + 1/2`` where ``u = W_x h + b_x >= 0`` and ``sigmoid(u)`` elsewhere; the output is
   ``W_o (S_t silu(W_g h))``.  It has a kernel of its own (a multiply-add per token and channel).
 
-The first three are the same recurrence (``csrc/recurrent.cu``), told by data how the decay is made (the
-matrix memory's normaliser is one more state column that is fed ones).  The
+* ``gated_delta``: the gated delta rule, whose write is the error of the state's own answer,
+  ``S <- diag(a_t) S``, ``u = b_t (v_t - S^T k_t)``, ``S <- S + k_t u^T``, ``o_t = S^T q_t`` with
+  ``b = sigmoid(W_b h)``; q, k and v pass a short causal convolution per channel and silu, q and
+  k are then unit vectors per head (``x / sqrt(sum x^2 + 1e-6)``) and q is scaled by
+  ``key_dim^(-1/2)``; q and k heads may be shared by groups of value heads.  The decay is
+  ``exp(-exp(A_log_h) softplus(z + dt_bias))`` with z one number per head (``W_a h``) or one per
+  head and key channel (``W_a2 W_a1 h``); each head's output is divided by its root mean square,
+  multiplied by a gain per value channel (shared by the heads) and by a gate, ``silu`` or
+  ``sigmoid`` of ``W_g h`` or of ``W_g2 W_g1 h``, and projected.
+
+The first three and the last are the same recurrence (``csrc/recurrent.cu``), told by data how the decay is made (the
+matrix memory's normaliser is one more state column that is fed ones) and whether the write is the delta rule's.  The
 state (and the convolution's last inputs) is 32-bit and lives in the request's fixed-size state
 slot of the cache manager, which clears a slot when a request is opened in it.  Everything
 behind the projections is computed in 32-bit.  Which rows belong to which request is read on
@@ -268,6 +278,145 @@ class MatrixMemory:
         self.o_proj(gated, x, accumulate=accumulate)
 
 
+class GatedDeltaRule:
+    """Kind ``gated_delta``.  Tensor roles: ``q``, ``k`` [groups * key_dim, hidden], ``v``
+    [heads * value_dim, hidden], their convolutions ``q_conv``, ``k_conv``, ``v_conv``
+    [channels, taps], ``b`` [heads, hidden], ``A_log`` [heads], ``norm`` [value_dim], ``o``;
+    the decay from ``a`` [heads, hidden] with ``dt_bias`` [heads], or from ``a1`` [r, hidden] and
+    ``a2`` [heads * key_dim, r] with ``dt_bias`` [heads * key_dim]; the gate from ``g``
+    [heads * value_dim, hidden] or from ``g1`` [r, hidden] and ``g2`` [heads * value_dim, r]
+    (the ranks are the tensors' own sizes).  ``gate_activation``: ``silu`` or ``sigmoid``."""
+
+    graph_safe = True
+    UNIT_FLOOR = 1e-6        # inside the root of the unit vectors
+
+    def __init__(self, spec: PartSpec, weights: Dict[str, torch.Tensor], dtype, device):
+        self.hidden = W = int(spec["hidden_size"])
+        self.heads = H = int(spec["num_heads"])
+        self.groups = G = int(spec.get("num_kv_heads") or H)
+        self.key_dim = K = int(spec["key_dim"])
+        self.value_dim = V = int(spec["value_dim"])
+        self.taps = int(spec["conv_taps"])
+        self.eps = float(spec["eps"])
+        self.gate_activation = spec.get("gate_activation", "silu")
+        if self.gate_activation not in ("silu", "sigmoid"):
+            raise ConfigError(f"gated_delta: gate_activation '{self.gate_activation}'")
+        if H % G or self.taps < 1:
+            raise ConfigError(f"gated_delta: {H} heads on {G} key heads, {self.taps} taps")
+        if K > 512:
+            raise ConfigError(f"gated_delta: key_dim {K}: the recurrence keeps at most 512 key "
+                              "channels of a state column in registers")
+        names = spec["tensors"]
+        t = {r: tensor_of(spec, r, weights) for r in names}
+        self.decay_per_channel = "a1" in names
+        self.gate_low_rank = "g1" in names
+        for a, b in (("a1", "a2"), ("g1", "g2")):
+            if (a in names) != (b in names) or (a in names and t[a].shape[0] != t[b].shape[1]):
+                raise ConfigError(f"gated_delta: the factors '{a}' and '{b}' come together and "
+                                  "agree on their rank")
+        # one product for everything that reads the mixer's input; every part starts a column
+        # range of whole 16-byte units
+        parts = [("q", t["q"]), ("k", t["k"]), ("v", t["v"]), ("b", t["b"]),
+                 ("a", t["a1"] if self.decay_per_channel else t["a"]),
+                 ("g", t["g1"] if self.gate_low_rank else t["g"])]
+        mats, self.col, at = [], {}, 0
+        for name, m in parts:
+            if name in ("b", "a", "g") and at % 4:
+                pad = 4 - at % 4
+                mats.append(torch.zeros(pad, W, dtype=m.dtype, device=m.device))
+                at += pad
+            self.col[name] = at
+            mats.append(m)
+            at += m.shape[0]
+        self.width_of = {name: m.shape[0] for name, m in parts}
+        self.in_proj = _padded_rows(mats, W)
+        self.conv_channels = 2 * G * K + H * V
+        if self.col["v"] != 2 * G * K or self.col["b"] < self.conv_channels:
+            raise ConfigError("gated_delta: q, k and v do not have the spec's sizes")
+        conv = [t[r + "_conv"] for r in ("q", "k", "v")]
+        for c, n in zip(conv, (G * K, G * K, H * V)):
+            if tuple(c.shape) != (n, self.taps):
+                raise ConfigError(f"gated_delta: a convolution of {list(c.shape)} for {n} "
+                                  f"channels and {self.taps} taps")
+        self.conv_weight = torch.cat([_f32(c, device) for c in conv]).contiguous()
+        self.decay_proj = Linear(t["a2"]) if self.decay_per_channel else None
+        self.gate_proj = Linear(t["g2"]) if self.gate_low_rank else None
+        self.rate_log = _f32(t["A_log"], device)
+        self.step_bias = _f32(t["dt_bias"], device)
+        if self.rate_log.numel() != H or \
+                self.step_bias.numel() != (H * K if self.decay_per_channel else H):
+            raise ConfigError("gated_delta: A_log has a number per head, dt_bias one per decay")
+        self.norm_weight = _f32(t["norm"], device)
+        if self.norm_weight.numel() != V:
+            raise ConfigError("gated_delta: the output norm has one weight per value channel of "
+                              "a head")
+        self.o_proj = Linear(t["o"])
+        self.state_floats = H * V * K
+
+    def cache_need(self):
+        """The matrix state of every head, then every convolved channel's last taps - 1 inputs."""
+        return FixedState((self.state_floats + self.conv_channels * (self.taps - 1),),
+                          torch.float32)
+
+    def streamed_weights(self):
+        extra = [p.weight for p in (self.decay_proj, self.gate_proj) if p is not None]
+        return [self.in_proj.weight, self.o_proj.weight] + extra
+
+    def _second(self, ctx: StepContext, proj: torch.Tensor, name: str, second: Linear,
+                out: torch.Tensor) -> None:
+        """out = second(the low-rank part ``name`` of proj), its operand rounded for 16-bit."""
+        low = proj[:, self.col[name]:self.col[name] + self.width_of[name]]
+        if ctx.dtype != torch.float32:
+            low16 = ctx.buffer("delta.low." + name, (ctx.rows, self.width_of[name]))
+            kernels.cast_rows(low, low16)
+            low = low16
+        second(low, out)
+
+    def run(self, ctx: StepContext, call: BoundCall, proj: torch.Tensor, x: torch.Tensor,
+            accumulate: bool) -> None:
+        """From the projections ``proj`` = [q | k | v | b | a | g] (float32) to the output."""
+        rows, H, G, K, V = ctx.rows, self.heads, self.groups, self.key_dim, self.value_dim
+        state = ctx.cache.state_of(call.cache_entry)
+        if state is None:
+            raise RuntimeError(f"run-order entry {call.index}: the recurrence needs a state slot")
+        seg = step_segments(ctx)
+        C = self.conv_channels
+        conv = ctx.buffer("delta.conv", (rows, C), torch.float32)
+        # (one tap keeps no inputs: a weight per channel, and the kernel reads no history)
+        history = state[:, self.state_floats:] if self.taps > 1 else state
+        kernels.causal_conv_silu(proj[:, :C], self.conv_weight, None, history, conv,
+                                 ctx.row_slot, seg)
+        beta = proj[:, self.col["b"]:self.col["b"] + H]
+        if self.decay_per_channel:
+            d = ctx.buffer("delta.decay", (rows, H * K), torch.float32)
+            self._second(ctx, proj, "a", self.decay_proj, d)
+            kernels.rate_decay(d, self.rate_log, self.step_bias, K)
+            kind, rate, bias = kernels.DECAY_VECTOR, None, None
+        else:
+            d = proj[:, self.col["a"]:self.col["a"] + H]
+            kind, rate, bias = kernels.DECAY_RATE_STEP, self.rate_log, self.step_bias
+        o = ctx.buffer("delta.o", (rows, H * V), torch.float32)
+        kernels.delta_recurrence(
+            conv[:, :G * K], conv[:, G * K:2 * G * K], conv[:, 2 * G * K:], d, beta, state, o,
+            ctx.row_slot, seg, H, G, K, V, kind, q_scale=K ** -0.5, unit_floor=self.UNIT_FLOOR,
+            rate_log=rate, step_bias=bias, n_requests=len(ctx.segments))
+        if self.gate_low_rank:
+            gate = ctx.buffer("delta.gate", (rows, H * V), torch.float32)
+            self._second(ctx, proj, "g", self.gate_proj, gate)
+        else:
+            gate = proj[:, self.col["g"]:self.col["g"] + H * V]
+        gated = ctx.buffer("delta.gated", (rows, H * V))
+        kernels.gated_group_norm(o, gate, self.norm_weight, gated, group=V, eps=self.eps,
+                                 gate_first=False, gate_activation=self.gate_activation)
+        self.o_proj(gated, x, accumulate=accumulate)
+
+    def forward(self, ctx: StepContext, call: BoundCall, h: torch.Tensor, x: torch.Tensor,
+                accumulate: bool = True) -> None:
+        proj = ctx.buffer("delta.proj", (ctx.rows, self.in_proj.out_features), torch.float32)
+        self.in_proj(h, proj)
+        self.run(ctx, call, proj, x, accumulate)
+
+
 class MinGru:
     graph_safe = True
 
@@ -321,6 +470,7 @@ class MinGru:
 
 
 register_part("mixer", "min_gru", MinGru, replace=True)
+register_part("mixer", "gated_delta", GatedDeltaRule, replace=True)
 register_part("mixer", "gla", GatedLinearAttention, replace=True)
 register_part("mixer", "mlstm", MatrixMemory, replace=True)
 register_part("mixer", "mamba2", StateSpaceMixer, replace=True)
