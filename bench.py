@@ -393,9 +393,9 @@ def main() -> int:
                          "(default 1)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="qwen3-8b")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "vunasun", "runidra", "pemolorn"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "vunasun", "runidra", "pemolorn", "pavatar"])
     ap.add_argument("--sizes", default="0.6b,8b",
-                    help="vunasun, runidra, pemolorn: the Qwen3 presets whose sizes both models take")
+                    help="vunasun, runidra, pemolorn, pavatar: the Qwen3 presets whose sizes the models take")
     ap.add_argument("--layers", type=int, default=None, help="build fewer layers (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=1024)
@@ -433,7 +433,7 @@ def main() -> int:
     pk = peaks()
     if args.workload == "vunasun":
         return vunasun_workload(args)
-    if args.workload in ("runidra", "pemolorn"):
+    if args.workload in ("runidra", "pemolorn", "pavatar"):
         return vunasun_workload(args, args.workload)
     cfg = preset_config(args.model, args.layers)
     full_layers = _full_layers(args.model)
@@ -452,7 +452,7 @@ def main() -> int:
 
 
 def vunasun_workload(args, design: str = "vunasun") -> int:
-    """Prompt and decode rates of Vunasun (or Runidra, or Pemolorn) models with random weights beside Qwen3
+    """Prompt and decode rates of Vunasun (or Runidra, Pemolorn, Pavatar) models with random weights beside Qwen3
     models of the same width, feed-forward width, heads and number of layers (``--layers``,
     default 8; ``--sizes``), and the design's own kernels one by one against the copy rate."""
     import importlib

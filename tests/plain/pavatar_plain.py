@@ -205,16 +205,23 @@ def routed_experts(h, t: Callable[[str], np.ndarray], f: dict):
 
 
 def close_calls(h, t, f: dict, margin: float) -> np.ndarray:
-    """Rows whose router would choose otherwise after a change of ``margin`` in a score."""
+    """Rows whose router would choose otherwise after a move of the router outputs by about
+    ``margin``: the last chosen expert and the best one not chosen lie closer in their choice
+    scores than ``margin`` times the larger of their scores (a move dz of an output moves its
+    score by about score * dz)."""
     r = f["router"]
     z = h @ t("router").T
     s = np.exp(z - z.max(axis=-1, keepdims=True))
     s /= s.sum(axis=-1, keepdims=True)
-    c = np.sort(s + t("correction"), axis=-1)[:, ::-1]
     top = int(r["top"])
-    if top >= c.shape[1]:
+    if top >= s.shape[1]:
         return np.zeros(h.shape[0], bool)
-    return (c[:, top - 1] - c[:, top]) < margin
+    c = s + t("correction")
+    order = np.argsort(-c, axis=-1, kind="stable")
+    a, b = order[:, top - 1:top], order[:, top:top + 1]
+    gap = np.take_along_axis(c, a, -1) - np.take_along_axis(c, b, -1)
+    size = np.maximum(np.take_along_axis(s, a, -1), np.take_along_axis(s, b, -1))
+    return (gap < margin * size)[:, 0]
 
 
 def forward(cfg: dict, tensors: Dict[str, np.ndarray], tokens, round_cache=lambda a: a,
