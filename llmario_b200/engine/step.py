@@ -12,6 +12,7 @@ step in one copy.
 """
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
@@ -414,8 +415,18 @@ class ModelRunner:
         torch.cuda.current_stream().synchronize()
         graph = torch.cuda.CUDAGraph()
         before = kernels.launches
-        with torch.cuda.graph(graph):
-            out = forward()
+        # Nothing may free device objects while the stream records: the collector is run now and
+        # kept off until the recording ends (a recording of a runner that has become garbage
+        # would otherwise be destroyed whenever the collector next runs, which ends this one).
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                out = forward()
+        finally:
+            if collecting:
+                gc.enable()
         recorded = kernels.launches - before
         self._graphs[key] = (gen, graph, out, recorded)
         self.counters["graphs_recorded"] += 1
