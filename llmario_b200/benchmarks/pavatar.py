@@ -90,11 +90,18 @@ def kernel_table(width: int = 4096, tokens: int = 2048, batch: int = 64, heads: 
     flush = torch.empty(160 << 20, dtype=torch.uint8, device=dev)
     rows_out: List[Dict[str, Any]] = []
 
-    def rec(name, us, nbytes, note=""):
-        rows_out.append({"kernel": name, "us": round(us, 2), "bytes": int(nbytes),
-                         "gb_s": round(nbytes / us / 1e3, 1),
-                         "frac_of_copy_peak": round(nbytes / (us * 1e-6) / (pk["hbm_gbs"] * 1e9), 3),
-                         "note": note})
+    # 32-bit operations a second of the CUDA cores: 148 SMs x 128 lanes x 2 at 1,965 MHz (nominal)
+    fp32_peak = 148 * 128 * 2 * 1.965e9
+
+    def rec(name, us, nbytes, note="", flops=0):
+        r = {"kernel": name, "us": round(us, 2), "bytes": int(nbytes),
+             "gb_s": round(nbytes / us / 1e3, 1),
+             "frac_of_copy_peak": round(nbytes / (us * 1e-6) / (pk["hbm_gbs"] * 1e9), 3),
+             "note": note}
+        if flops:
+            r["fp32_tflops"] = round(flops / us / 1e6, 2)
+            r["frac_of_fp32_peak"] = round(flops / (us * 1e-6) / fp32_peak, 3)
+        rows_out.append(r)
 
     f32 = lambda *s: torch.randn(*s, dtype=torch.float32, device=dev)
     b16 = lambda *s: torch.randn(*s, dtype=torch.bfloat16, device=dev)
@@ -122,24 +129,29 @@ def kernel_table(width: int = 4096, tokens: int = 2048, batch: int = 64, heads: 
             q, k, v, step, beta, state, o, row_slot, seg, H, G, K, V, kernels.DECAY_RATE_STEP,
             q_scale=K ** -0.5, unit_floor=1e-6, rate_log=rate, step_bias=bias, n_requests=live),
             flush=flush)
-        rec(f"delta rule, a decay per head, {H} heads of {K} x {V} ({label})", us, io + rows * H * 8)
+        # per state element and token: the delta rule a multiply and three multiply-adds, the
+        # plain write two multiply-adds
+        cells = rows * H * K * V
+        rec(f"delta rule, a decay per head, {H} heads of {K} x {V} ({label})", us, io + rows * H * 8,
+            flops=7.0 * cells)
         state.zero_()
         us = _time(lambda: kernels.delta_recurrence(
             q, k, v, decay, beta, state, o, row_slot, seg, H, G, K, V, kernels.DECAY_VECTOR,
             q_scale=K ** -0.5, unit_floor=1e-6, n_requests=live), flush=flush)
-        rec(f"delta rule, a decay per key channel ({label})", us, io + rows * H * (K + 1) * 4)
+        rec(f"delta rule, a decay per key channel ({label})", us, io + rows * H * (K + 1) * 4,
+            flops=7.0 * cells)
         state.zero_()
         us = _time(lambda: kernels.linear_recurrence(
             q, k, v, step, state, o, row_slot, seg, H, G, K, V, kernels.DECAY_RATE_STEP,
             rate_log=rate, step_bias=bias, n_requests=live), flush=flush)
         rec(f"linear recurrence, a decay per head, the state-space mixer's ({label})", us,
-            io + rows * H * 4)
+            io + rows * H * 4, flops=4.0 * cells)
         state.zero_()
         us = _time(lambda: kernels.linear_recurrence(
             q, k, v, decay, state, o, row_slot, seg, H, G, K, V, kernels.DECAY_VECTOR,
             q_scale=K ** -0.5, n_requests=live), flush=flush)
         rec(f"linear recurrence, a decay per key channel, gated linear attention's ({label})", us,
-            io + rows * H * K * 4)
+            io + rows * H * K * 4, flops=4.0 * cells)
         # ---- the decay per key channel from the projected step
         z, kb = f32(rows, H * K), f32(H * K)
         us = _time(lambda: kernels.rate_decay(z, rate, kb, K), flush=flush)
@@ -196,11 +208,12 @@ def main(argv=None) -> int:
     ap.add_argument("--layers", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--kernels", action="store_true", help="only the table of kernels")
+    ap.add_argument("--tokens", type=int, default=2048, help="tokens of the table's prompt portion")
     a = ap.parse_args(argv)
     rec: Dict[str, Any] = {}
     if not a.kernels:
         rec = compare([s for s in a.sizes.split(",") if s], a.layers, batch=a.batch)
-    rec["kernels"] = kernel_table()
+    rec["kernels"] = kernel_table(tokens=a.tokens, context=max(4096, a.tokens))
     json.dump(rec, sys.stdout, indent=1)
     print()
     return 0
