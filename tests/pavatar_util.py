@@ -75,7 +75,8 @@ CONFIGS: Dict[str, dict] = {
     # keys and values of one size, no temperature, no blending: the store of the standard layers
     "attn_plain": config([attention(heads=4, kv_heads=4, dim=32, vdim=32, every=0, v_mix=False),
                           attention(heads=2, kv_heads=1, dim=64, vdim=64, every=0, v_mix=False,
-                                    mlp=moe())]),
+                                    mlp=moe()),
+                          attention(heads=3, kv_heads=3, dim=16, vdim=24, every=0, v_mix=False)]),
     # three layers blend values (the first one's), one between them does not; values longer
     # than keys; a temperature that steps at every token and one that never does
     "attn_blend": config([attention(heads=2, kv_heads=2, dim=16, vdim=24, every=1, coef=0.05),
@@ -109,6 +110,14 @@ CONFIGS: Dict[str, dict] = {
                           attention(heads=4, kv_heads=1, dim=64, vdim=64, every=9, mlp=moe(4, 2, 32)),
                           attention(heads=16, kv_heads=1, dim=64, vdim=64, every=4)],
                          width=128, vocab=80),
+    # keys shorter than values whose size the tensor-core kernels have: the cache's rows are the
+    # values', the queries and keys are padded
+    "keys_shorter": config([attention(heads=4, kv_heads=2, dim=32, vdim=64, every=6),
+                            parallel(heads=2, kv_heads=2, dim=48, vdim=64, rot=12,
+                                     right=delta_sizes(heads=2, kv_heads=1, dim=64, vdim=64, conv=3,
+                                                       rank=8), mlp=moe(3, 2, 48)),
+                            attention(heads=8, kv_heads=2, dim=32, vdim=64, every=0)],
+                           width=72, vocab=70),
     # all of them, in an order of their own
     "mix": config([attention(every=11, mlp=moe()),
                    delta(mlp=moe(4, 2, 32)),
