@@ -6,6 +6,7 @@ or a library that cannot be built, is an error.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional, Tuple
@@ -121,8 +122,6 @@ def _signatures():
         "llm_channel_gate": [P, I, P, I, I, I, I, P],
         "llm_delta_recurrence": [P, I, P, I, P, I, P, I, P, I, P, P, F, I, F, P, L, P, I, P, P, I,
                                  I, I, I, I, I, I, I, P],
-        "llm_delta_recurrence_grouped": [P, I, P, I, P, I, P, I, P, I, P, P, F, I, F, P, L, P, I, P,
-                                         P, I, I, I, I, I, I, I, I, P, L, P],
         "llm_rate_decay": [P, P, P, I, I, I, P],
         "llm_moe_router_scaled": [P, I, P, P, P, I, I, I, I, I, I, I, P, P, P, F, P],
         "llm_moe_route_scaled": [P, I, I, I, I, I, P, P, P, F, P],
@@ -529,8 +528,7 @@ def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d: torch
                      key_dim: int, value_dim: int, kind: int, q_scale: float = 1.0,
                      unit_floor: Optional[float] = None,
                      rate_log: Optional[torch.Tensor] = None,
-                     step_bias: Optional[torch.Tensor] = None, n_requests: int = 0,
-                     work: Optional[torch.Tensor] = None) -> None:
+                     step_bias: Optional[torch.Tensor] = None, n_requests: int = 0) -> None:
     """The gated delta rule per request and head over the rows of the step in order:
     ``S <- diag(a_t) S``, ``u = sigmoid(beta_t) (v_t - S^T k_t)``, ``S <- S + k_t u^T``,
     ``o_t = S^T q_t``.  Tensors, state and ``seg`` as in :func:`linear_recurrence`; ``beta``
@@ -538,38 +536,20 @@ def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d: torch
     [rows, heads * key_dim] is the decay; DECAY_RATE_STEP: ``d`` [rows, heads] and
     ``a = exp(-exp(rate_log[h]) softplus(d + step_bias[h]))`` for every key channel of head h.
     ``unit_floor`` (not None): q and k of every head are first divided by
-    ``sqrt(sum of squares + unit_floor)``; q is then multiplied by ``q_scale``.
-    ``work`` (float32, at least :func:`delta_work_floats` elements): room for what portions of
-    prompts need to go four tokens at a time (68 to 256 key channels, a multiple of four);
-    without it, and for single tokens, every row goes token by token.  The two ways differ by
-    rounding only."""
-    _cuda(q, k, v, d, beta, state, out, row_slot, seg, rate_log, step_bias, work)
-    assert work is None or (work.dtype == torch.float32 and work.is_contiguous())
+    ``sqrt(sum of squares + unit_floor)``; q is then multiplied by ``q_scale``."""
+    _cuda(q, k, v, d, beta, state, out, row_slot, seg, rate_log, step_bias)
     for t in (q, k, v, d, beta, state, out):
         assert t.dtype == torch.float32 and t.stride(-1) == 1
     rows = out.shape[0]
     assert state.dim() == 2 and state.shape[1] >= heads * value_dim * key_dim
     assert kind in (DECAY_VECTOR, DECAY_RATE_STEP)
-    _check(lib().llm_delta_recurrence_grouped(
+    _check(lib().llm_delta_recurrence(
         _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(d), d.stride(0),
         _ptr(beta), beta.stride(0), _ptr(rate_log), _ptr(step_bias), float(q_scale),
         int(unit_floor is not None), float(unit_floor or 0.0), _ptr(state), state.stride(0),
         _ptr(out), out.stride(0), _ptr(seg), _ptr(row_slot), rows, int(n_requests),
-        int(seg is None), heads, groups, key_dim, value_dim, kind, _ptr(work),
-        work.numel() if work is not None else 0, _stream()),
+        int(seg is None), heads, groups, key_dim, value_dim, kind, _stream()),
         f"delta_recurrence (key_dim {key_dim})")
-    global launches
-    if work is not None and seg is not None and delta_work_floats(rows, heads, key_dim) \
-            and work.numel() >= delta_work_floats(rows, heads, key_dim):
-        launches += 2      # the groups' preparation and their walk are launches of their own
-
-
-def delta_work_floats(rows: int, heads: int, key_dim: int) -> int:
-    """Elements of the ``work`` buffer with which :func:`delta_recurrence` takes the rows of a
-    step four tokens at a time, 0 when it has no such form for this many key channels."""
-    if not (64 < key_dim <= 256 and key_dim % 4 == 0):
-        return 0
-    return rows * heads * (4 * key_dim + 41)
 
 
 def causal_conv_silu(src: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
@@ -834,13 +814,32 @@ def force_pair_k_ranges(n: int) -> None:
     l.llm_set_pair_ksplits(int(n))
 
 
+_dependent_launch = True
+
+
 def use_dependent_launch(on: bool) -> None:
     """Whether kernels are launched as programmatic dependents of the one before them (the
-    default) or wait for its end.  For measurements."""
+    default) or wait for its end.  For measurements, and see :func:`plain_stream_order`."""
+    global _dependent_launch
     l = lib()
     l.llm_set_pdl.argtypes = [c_int]
     l.llm_set_pdl.restype = None
     l.llm_set_pdl(int(on))
+    _dependent_launch = bool(on)
+
+
+@contextlib.contextmanager
+def plain_stream_order():
+    """Kernels launched inside start only when the kernel before them has ended, whatever
+    :func:`use_dependent_launch` says; the setting is put back afterwards."""
+    was = _dependent_launch
+    if was:
+        use_dependent_launch(False)
+    try:
+        yield
+    finally:
+        if was:
+            use_dependent_launch(True)
 
 
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, half: int = 0,

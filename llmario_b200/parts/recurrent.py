@@ -374,7 +374,23 @@ class GatedDeltaRule:
 
     def run(self, ctx: StepContext, call: BoundCall, proj: torch.Tensor, x: torch.Tensor,
             accumulate: bool) -> None:
-        """From the projections ``proj`` = [q | k | v | b | a | g] (float32) to the output."""
+        """From the projections ``proj`` = [q | k | v | b | a | g] (float32) to the output.
+
+        With low-rank factors a step that holds portions of prompts launches this mixer's
+        kernels in plain stream order.  As programmatic dependents of one another (operand
+        rounded, second product of many rows, decay or gate + norm, with the walk of the
+        recurrence between them) such steps stopped making progress now and then on models of
+        a width of 1,024 (four of six runs of a model of eight such layers; none of seven in
+        plain stream order; no bounded wait reported).  Steps of single tokens, whose products
+        are the kernels for few rows, keep the dependent launches."""
+        if (self.decay_per_channel or self.gate_low_rank) and ctx.rows != len(ctx.segments):
+            with kernels.plain_stream_order():
+                self._run(ctx, call, proj, x, accumulate)
+        else:
+            self._run(ctx, call, proj, x, accumulate)
+
+    def _run(self, ctx: StepContext, call: BoundCall, proj: torch.Tensor, x: torch.Tensor,
+             accumulate: bool) -> None:
         rows, H, G, K, V = ctx.rows, self.heads, self.groups, self.key_dim, self.value_dim
         state = ctx.cache.state_of(call.cache_entry)
         if state is None:
@@ -396,14 +412,10 @@ class GatedDeltaRule:
             d = proj[:, self.col["a"]:self.col["a"] + H]
             kind, rate, bias = kernels.DECAY_RATE_STEP, self.rate_log, self.step_bias
         o = ctx.buffer("delta.o", (rows, H * V), torch.float32)
-        # (portions of prompts go four tokens at a time where the kernels have that form)
-        work = None
-        if seg is not None and kernels.delta_work_floats(rows, H, K):
-            work = ctx.buffer("delta.work", (kernels.delta_work_floats(rows, H, K),), torch.float32)
         kernels.delta_recurrence(
             conv[:, :G * K], conv[:, G * K:2 * G * K], conv[:, 2 * G * K:], d, beta, state, o,
             ctx.row_slot, seg, H, G, K, V, kind, q_scale=K ** -0.5, unit_floor=self.UNIT_FLOOR,
-            rate_log=rate, step_bias=bias, n_requests=len(ctx.segments), work=work)
+            rate_log=rate, step_bias=bias, n_requests=len(ctx.segments))
         if self.gate_low_rank:
             gate = ctx.buffer("delta.gate", (rows, H * V), torch.float32)
             self._second(ctx, proj, "g", self.gate_proj, gate)
