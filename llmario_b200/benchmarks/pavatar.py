@@ -125,10 +125,13 @@ def kernel_table(width: int = 4096, tokens: int = 2048, batch: int = 64, heads: 
         beta, step, rate, bias = f32(rows, H), f32(rows, H), f32(H) - 3.0, f32(H)
         decay = torch.rand(rows, H * K, dtype=torch.float32, device=dev) * 0.1 + 0.9
         io = rows * (2 * G * K + 2 * H * V) * 4 + 2 * live * H * V * K * 4
+        # (a portion goes four tokens at a time: preparation, groups and the rows left over)
+        work = None if single else torch.empty(kernels.delta_work_floats(rows, H, K),
+                                               dtype=torch.float32, device=dev)
         us = _time(lambda: kernels.delta_recurrence(
             q, k, v, step, beta, state, o, row_slot, seg, H, G, K, V, kernels.DECAY_RATE_STEP,
-            q_scale=K ** -0.5, unit_floor=1e-6, rate_log=rate, step_bias=bias, n_requests=live),
-            flush=flush)
+            q_scale=K ** -0.5, unit_floor=1e-6, rate_log=rate, step_bias=bias, n_requests=live,
+            work=work), flush=flush)
         # per state element and token: the delta rule a multiply and three multiply-adds, the
         # plain write two multiply-adds
         cells = rows * H * K * V
@@ -137,9 +140,17 @@ def kernel_table(width: int = 4096, tokens: int = 2048, batch: int = 64, heads: 
         state.zero_()
         us = _time(lambda: kernels.delta_recurrence(
             q, k, v, decay, beta, state, o, row_slot, seg, H, G, K, V, kernels.DECAY_VECTOR,
-            q_scale=K ** -0.5, unit_floor=1e-6, n_requests=live), flush=flush)
+            q_scale=K ** -0.5, unit_floor=1e-6, n_requests=live, work=work), flush=flush)
         rec(f"delta rule, a decay per key channel ({label})", us, io + rows * H * (K + 1) * 4,
             flops=7.0 * cells)
+        if not single:
+            state.zero_()
+            us = _time(lambda: kernels.delta_recurrence(
+                q, k, v, decay, beta, state, o, row_slot, seg, H, G, K, V, kernels.DECAY_VECTOR,
+                q_scale=K ** -0.5, unit_floor=1e-6, n_requests=live), flush=flush)
+            rec(f"delta rule, a decay per key channel, token by token ({label})", us,
+                io + rows * H * (K + 1) * 4, flops=7.0 * cells)
+        del work
         state.zero_()
         us = _time(lambda: kernels.linear_recurrence(
             q, k, v, step, state, o, row_slot, seg, H, G, K, V, kernels.DECAY_RATE_STEP,

@@ -121,11 +121,22 @@ static inline int launched_many_blocks(int rc, long long blocks) {
   return rc;
 }
 
+// 1: the next launch starts in plain stream order, whatever g_llm_pdl says (then 0 again).  A
+// kernel that is launched as a programmatic dependent becomes resident as soon as the kernel before
+// it allows it and waits there for that kernel's end.  Behind a kernel that runs for a millisecond
+// with fewer than two warps per scheduler (the walk of a recurrence over a prompt) the waiting
+// blocks cost the walk half of its rate (measured: 1,345 us against 607 us for the delta rule over
+// 2,048 tokens), so such a kernel asks for a plain launch of whatever follows it.
+extern int g_llm_next_plain;
+static inline void next_launch_plain() { g_llm_next_plain = 1; }
+
 // Launch a kernel that calls pdl_wait() itself.
 template <typename... KArgs, typename... Args>
 static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                              cudaStream_t stream, Args... args) {
   g_llm_after_rotation = 0;
+  const int plain = g_llm_next_plain;
+  g_llm_next_plain = 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -135,6 +146,6 @@ static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = g_llm_pdl ? 1 : 0;
+  cfg.numAttrs = g_llm_pdl && !plain ? 1 : 0;
   return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }

@@ -3,6 +3,7 @@
 
 int g_llm_pdl = 1;
 int g_llm_after_rotation = 0;
+int g_llm_next_plain = 0;
 LLM_EXPORT void llm_set_pdl(int on) { g_llm_pdl = on ? 1 : 0; }
 
 // x[t][:] = table[token[t]][:] * scale   (residual stream is 32-bit in every mode)
@@ -540,9 +541,11 @@ LLM_EXPORT int llm_head_gate(void* out, int dtype, float* gate, int gate_stride,
   if (items <= 0) return 0;
   const int blocks = (int)((items + 3) / 4);
   if (dtype == LLM_F32)
-    return launch_pdl(head_gate_kernel<float>, blocks, 128, 0, stream, (float*)out, gate, gate_stride, rows, H, hd, clear);
+    return launched_many_blocks(launch_pdl(head_gate_kernel<float>, blocks, 128, 0, stream, (float*)out, gate,
+                                           gate_stride, rows, H, hd, clear), blocks);
   if (dtype == LLM_BF16)
-    return launch_pdl(head_gate_kernel<bf16>, blocks, 128, 0, stream, (bf16*)out, gate, gate_stride, rows, H, hd, clear);
+    return launched_many_blocks(launch_pdl(head_gate_kernel<bf16>, blocks, 128, 0, stream, (bf16*)out, gate,
+                                           gate_stride, rows, H, hd, clear), blocks);
   return LLM_ERR_UNSUPPORTED;
 }
 
@@ -568,7 +571,7 @@ LLM_EXPORT int llm_channel_gate(void* out, int dtype, float* gate, int gate_stri
   const long long total = (long long)rows * cols;
   if (total <= 0) return 0;
   const int blocks = (int)((total + 255) / 256 < 4736 ? (total + 255) / 256 : 4736);
-  // (a kernel of many blocks in front of the output projection: see launched_many_blocks)
+  // (it stands in front of the output projection: see launched_many_blocks)
   if (dtype == LLM_F32)
     return launched_many_blocks(launch_pdl(channel_gate_kernel<float>, blocks, 256, 0, stream, (float*)out, gate,
                                            gate_stride, cols, total, clear), blocks);

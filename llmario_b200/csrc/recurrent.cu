@@ -79,6 +79,7 @@ struct ScanArgs {
   // `unit`: q and k of every head are divided by sqrt(sum of squares + unit_floor) first
   const float* beta; int beta_stride;
   int unit; float unit_floor;
+  int tail_only;        // only the last (rows of the request) % 4 rows: the others went in groups of four
 };
 
 constexpr int SCAN_THREADS = 128;
@@ -135,6 +136,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_recurrence_kernel(const S
     if (slot < 0) return;
     first = a.seg[SEG * slot], end = a.seg[SEG * slot + 1];
   }
+  if (a.tail_only) first = end - ((end - first) & 3);
   if (end <= first) return;
   const int K = a.K, V = a.V, g = h / (a.H / a.G);
   const int j0 = blockIdx.z * COLS;
@@ -771,6 +773,310 @@ LLM_EXPORT int llm_segment_table(const int* row_slot, int rows, int* seg, int n_
   return launch_pdl(segment_table_kernel, 1, 256, 0, stream, row_slot, rows, seg, n_slots);
 }
 
+
+// ---- the delta rule over portions of prompts, four tokens at a time.
+// With a_m the decay of token m of a group 0..3, A_j = a_0 .. a_j and D_ij = a_(i+1) .. a_j (channel
+// by channel), the state S before the group answers token j's key with S^T (A_j k_j) plus, for every
+// earlier token i of the group, u_i G_ij with G_ij = sum_e k_i D_ij k_j; its query likewise with
+// H_ij = sum_e k_i D_ij q_j (i <= j); and after the group S = A_3 S + sum_i (D_i3 k_i) u_i^T.  So the
+// writes u_0 .. u_3 follow from the state's eight answers by a triangular system whose coefficients
+// are dot products over the key channels.  Everything a group needs besides the state is made once
+// per (request, head, group) by delta_prepare_kernel, in parallel over the tokens: A_j q_j (qa),
+// A_j k_j (ka), D_j3 k_j (kh), A_3 (at, for a decay per channel; else the 41st coefficient), the
+// coefficients coef[i][0][j] = G_ij (j > i) and coef[i][1][j] = H_ij (j >= i), zero elsewhere, and
+// the sigmoid of the write strength (bs); q and k are made unit vectors on the way.  A group's data
+// stand at its first row.  delta_groups_kernel then walks the groups of a request in order.
+constexpr int GROUP_COEF = 40;      // 32 coefficients, the scalar A_3, padding to whole 16 bytes
+constexpr int PREPARE_WARPS = 8, PREPARE_SPLITS = 8;
+struct GroupArgs {
+  const float* q; int q_stride; const float* k; int k_stride; const float* v; int v_stride;
+  const float* d; int d_stride;          // DECAY_VECTOR: the decay [row][h * K + i]; DECAY_RATE_STEP: [row][h]
+  const float* beta; int beta_stride;
+  const float* p0; const float* p1;
+  float q_scale; int unit; float unit_floor;
+  const int* seg;
+  int H, G, K, V, kind;
+  float *qa, *ka, *kh, *at, *coef, *bs;  // [rows][H][K] (four of them), [rows][H][GROUP_COEF], [rows][H]
+  float* state; long long state_stride; float* out; int out_stride;
+};
+
+__global__ void __launch_bounds__(PREPARE_WARPS * 32) delta_prepare_kernel(const GroupArgs a) {
+  pdl_trigger();
+  pdl_wait();
+  const int slot = a.seg[SEG * blockIdx.x + 2];
+  if (slot < 0) return;
+  const int first = a.seg[SEG * slot], end = a.seg[SEG * slot + 1];
+  const int n_groups = (end - first) >> 2;
+  const int h = blockIdx.y, g = h / (a.H / a.G), K = a.K, lane = threadIdx.x & 31;
+  const bool vec = a.kind == DECAY_VECTOR;
+  const float rate = vec ? 0.f : expf(a.p0[h]), bias = vec ? 0.f : a.p1[h];
+  for (int mc = blockIdx.z * PREPARE_WARPS + (threadIdx.x >> 5); mc < n_groups; mc += PREPARE_WARPS * gridDim.z) {
+    const int r0 = first + 4 * mc;
+    const float *qp[4], *kp[4], *dp[4];
+    float as[4] = {1.f, 1.f, 1.f, 1.f};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      qp[j] = a.q + (size_t)(r0 + j) * a.q_stride + g * K, kp[j] = a.k + (size_t)(r0 + j) * a.k_stride + g * K;
+      dp[j] = a.d + (size_t)(r0 + j) * a.d_stride + (vec ? h * K : h);
+      if (!vec) as[j] = expf(-rate * softplus_f(dp[j][0] + bias));
+    }
+    float acc[24];      // 0-3 |q_j|^2, 4-7 |k_j|^2, 8-13 G_ij (i < j), 14-23 H_ij (i <= j), both by rows
+#pragma unroll
+    for (int x = 0; x < 24; ++x) acc[x] = 0.f;
+    for (int i = lane; i < K; i += 32) {
+      float qv[4], kv[4], av[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        qv[j] = qp[j][i], kv[j] = kp[j][i], av[j] = vec ? dp[j][i] : as[j];
+        acc[j] = fmaf(qv[j], qv[j], acc[j]);
+        acc[4 + j] = fmaf(kv[j], kv[j], acc[4 + j]);
+      }
+      int gi = 8, hi = 14;
+#pragma unroll
+      for (int ii = 0; ii < 4; ++ii) {
+        float dk = kv[ii];
+        acc[hi] = fmaf(dk, qv[ii], acc[hi]), ++hi;
+#pragma unroll
+        for (int jj = ii + 1; jj < 4; ++jj) {
+          dk *= av[jj];
+          acc[gi] = fmaf(dk, kv[jj], acc[gi]), ++gi;
+          acc[hi] = fmaf(dk, qv[jj], acc[hi]), ++hi;
+        }
+      }
+    }
+#pragma unroll
+    for (int x = 0; x < 24; ++x) acc[x] = warp_sum(acc[x]);
+    float fq[4], fk[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      fq[j] = (a.unit ? 1.0f / sqrtf(acc[j] + a.unit_floor) : 1.f) * a.q_scale;
+      fk[j] = a.unit ? 1.0f / sqrtf(acc[4 + j] + a.unit_floor) : 1.f;
+    }
+    if (lane == 0) {
+      float* cf = a.coef + ((size_t)r0 * a.H + h) * GROUP_COEF;
+      int gi = 8, hi = 14;
+#pragma unroll
+      for (int ii = 0; ii < 4; ++ii) {
+#pragma unroll
+        for (int jj = 0; jj < ii; ++jj) cf[ii * 8 + jj] = 0.f, cf[ii * 8 + 4 + jj] = 0.f;
+        cf[ii * 8 + ii] = 0.f;
+        cf[ii * 8 + 4 + ii] = acc[hi] * fk[ii] * fq[ii], ++hi;
+#pragma unroll
+        for (int jj = ii + 1; jj < 4; ++jj) {
+          cf[ii * 8 + jj] = acc[gi] * fk[ii] * fk[jj], ++gi;
+          cf[ii * 8 + 4 + jj] = acc[hi] * fk[ii] * fq[jj], ++hi;
+        }
+      }
+      cf[32] = as[0] * as[1] * as[2] * as[3];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        a.bs[(size_t)(r0 + j) * a.H + h] = 1.f / (1.f + expf(-a.beta[(size_t)(r0 + j) * a.beta_stride + h]));
+    }
+    for (int i = lane; i < K; i += 32) {
+      float qv[4], kv[4], av[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) qv[j] = qp[j][i] * fq[j], kv[j] = kp[j][i] * fk[j], av[j] = vec ? dp[j][i] : as[j];
+      float up = 1.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        up *= av[j];
+        const size_t at = ((size_t)(r0 + j) * a.H + h) * K + i;
+        a.qa[at] = up * qv[j], a.ka[at] = up * kv[j];
+      }
+      float down = 1.f;
+#pragma unroll
+      for (int j = 3; j >= 0; --j) {
+        a.kh[((size_t)(r0 + j) * a.H + h) * K + i] = down * kv[j];
+        down *= av[j];
+      }
+      if (vec) a.at[((size_t)r0 * a.H + h) * K + i] = up;
+    }
+  }
+}
+
+// A block owns sixteen value channels of one head of one request, as in the kernel above with a
+// whole warp per group of four columns.  Per group of four tokens the thirty-two sums (the state's
+// answers for four keys and four queries, in four columns) are made in one pass and summed over
+// the warp so that lane (kind, token j, column c) = (bit 4, bits 3-2, bits 1-0) ends up with one of
+// them; four rounds hand the writes on (the lanes of a key's sum turn it into the write when its
+// round comes, the others add what the write does to their sum); then every lane takes all sixteen
+// writes and brings its part of the state to the end of the group.  Two groups are staged at a
+// time by asynchronous copies, two stages in flight.
+template <int NF, bool VEC>
+__global__ void __launch_bounds__(SCAN_THREADS) delta_groups_kernel(const GroupArgs a) {
+  constexpr int L = 32, KP = 4 * L * NF, COLS = 4 * (SCAN_THREADS / 32);
+  constexpr int TC = NF == 1 ? 8 : 4, NG = TC / 4;
+  __shared__ __align__(16) float qa_s[2][TC][KP];
+  __shared__ __align__(16) float ka_s[2][TC][KP];
+  __shared__ __align__(16) float kh_s[2][TC][KP];
+  __shared__ __align__(16) float at_s[2][VEC ? NG : 1][VEC ? KP : 4];
+  __shared__ __align__(16) float coef_s[2][NG][GROUP_COEF];
+  __shared__ __align__(16) float v_s[2][TC][COLS];
+  __shared__ float b_s[2][TC];
+  pdl_trigger();
+  pdl_wait();
+  const int slot = a.seg[SEG * blockIdx.x + 2];
+  if (slot < 0) return;
+  const int first = a.seg[SEG * slot];
+  const int end = first + ((a.seg[SEG * slot + 1] - first) & ~3);       // whole groups only
+  if (end <= first) return;
+  const int h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int K = a.K, V = a.V, H = a.H;
+  const int j0 = blockIdx.z * COLS, c0 = warp * 4, jc = j0 + c0;
+  float* sbase = a.state + (size_t)slot * a.state_stride + (size_t)h * V * K;
+  const bool k4 = ((uintptr_t)sbase & 15) == 0;       // (K is a multiple of four here)
+  for (int idx = tid; idx < 2 * TC * (KP - K); idx += SCAN_THREADS) {
+    const int st = idx / (TC * (KP - K)), rem = idx - st * TC * (KP - K);
+    const int tt = rem / (KP - K), i = K + rem - tt * (KP - K);
+    qa_s[st][tt][i] = 0.f, ka_s[st][tt][i] = 0.f, kh_s[st][tt][i] = 0.f;
+    if (VEC && (tt & 3) == 0) at_s[st][tt >> 2][i] = 1.f;
+  }
+  auto fetch = [&](int st, int t0) {
+    const int n_tok = min(TC, end - t0), k4n = K >> 2;
+    for (int idx = tid; idx < n_tok * k4n; idx += SCAN_THREADS) {
+      const int tt = idx / k4n, i = (idx - tt * k4n) << 2;
+      const size_t at = ((size_t)(t0 + tt) * H + h) * K + i;
+      cp_async16(&qa_s[st][tt][i], a.qa + at);
+      cp_async16(&ka_s[st][tt][i], a.ka + at);
+      cp_async16(&kh_s[st][tt][i], a.kh + at);
+      if (VEC && (tt & 3) == 0) cp_async16(&at_s[st][tt >> 2][i], a.at + at);
+    }
+    for (int idx = tid; idx < (n_tok >> 2) * (GROUP_COEF / 4); idx += SCAN_THREADS) {
+      const int gq = idx / (GROUP_COEF / 4), i = (idx - gq * (GROUP_COEF / 4)) << 2;
+      cp_async16(&coef_s[st][gq][i], a.coef + ((size_t)(t0 + 4 * gq) * H + h) * GROUP_COEF + i);
+    }
+    for (int idx = tid; idx < n_tok * COLS; idx += SCAN_THREADS) {
+      const int tt = idx / COLS, cc = idx - tt * COLS;
+      if (j0 + cc < V) cp_async4(&v_s[st][tt][cc], a.v + (size_t)(t0 + tt) * a.v_stride + h * V + j0 + cc);
+      else v_s[st][tt][cc] = 0.f;
+    }
+    for (int tt = tid; tt < n_tok; tt += SCAN_THREADS) cp_async4(&b_s[st][tt], a.bs + (size_t)(t0 + tt) * H + h);
+    cp_async_commit();
+  };
+  fetch(0, first);
+  float s[NF][4][4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const bool live = jc + c < V;
+    const float* srow = sbase + (size_t)(live ? jc + c : 0) * K;
+#pragma unroll
+    for (int n = 0; n < NF; ++n) {
+      const int i0 = 4 * (lane + L * n);
+      if (live && k4 && i0 + 3 < K) {
+        const float4 t = *reinterpret_cast<const float4*>(srow + i0);
+        s[n][0][c] = t.x, s[n][1][c] = t.y, s[n][2][c] = t.z, s[n][3][c] = t.w;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[n][e][c] = (live && i0 + e < K) ? srow[i0 + e] : 0.f;
+      }
+    }
+  }
+  const int kind = lane >> 4, j_mine = (lane >> 2) & 3, c_mine = lane & 3;
+  int st = 0;
+  for (int t0 = first; t0 < end; t0 += TC, st ^= 1) {
+    const int n_groups = min(TC, end - t0) >> 2;
+    if (t0 + TC < end) {
+      fetch(st ^ 1, t0 + TC);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    for (int mc = 0; mc < n_groups; ++mc) {
+      const int tb = 4 * mc;
+      float v[32];
+#pragma unroll
+      for (int x = 0; x < 32; ++x) v[x] = 0.f;
+#pragma unroll
+      for (int n = 0; n < NF; ++n) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float4 kk = *reinterpret_cast<const float4*>(&ka_s[st][tb + j][4 * (lane + L * n)]);
+          const float4 qq = *reinterpret_cast<const float4*>(&qa_s[st][tb + j][4 * (lane + L * n)]);
+          const float ke[4] = {kk.x, kk.y, kk.z, kk.w}, qe[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              v[4 * j + c] = fmaf(s[n][e][c], ke[e], v[4 * j + c]);
+              v[16 + 4 * j + c] = fmaf(s[n][e][c], qe[e], v[16 + 4 * j + c]);
+            }
+        }
+      }
+#pragma unroll
+      for (int half = 16; half > 0; half >>= 1) {
+        const bool hi = (lane & half) != 0;
+#pragma unroll
+        for (int x = 0; x < half; ++x) {
+          const float send = hi ? v[x] : v[x + half], keep = hi ? v[x + half] : v[x];
+          v[x] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+        }
+      }
+      float val = v[0];
+      const float v_mine = v_s[st][tb + j_mine][c0 + c_mine], b_mine = b_s[st][tb + j_mine];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float u_cand = b_mine * (v_mine - val);
+        const float u_j = __shfl_sync(0xffffffffu, u_cand, (j << 2) | c_mine);
+        if (kind == 0 && j_mine == j) val = u_cand;
+        val = fmaf(coef_s[st][mc][j * 8 + kind * 4 + j_mine], u_j, val);
+      }
+      if (kind == 1 && jc + c_mine < V)
+        a.out[(size_t)(t0 + tb + j_mine) * a.out_stride + h * V + jc + c_mine] = val;
+      float ue[4][4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) ue[j][c] = __shfl_sync(0xffffffffu, val, (j << 2) | c);
+      const float at1 = VEC ? 1.f : coef_s[st][mc][32];
+#pragma unroll
+      for (int n = 0; n < NF; ++n) {
+        float4 aa = make_float4(at1, at1, at1, at1);
+        if (VEC) aa = *reinterpret_cast<const float4*>(&at_s[st][mc][4 * (lane + L * n)]);
+        const float ae[4] = {aa.x, aa.y, aa.z, aa.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) s[n][e][c] *= ae[e];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float4 kk = *reinterpret_cast<const float4*>(&kh_s[st][tb + j][4 * (lane + L * n)]);
+          const float ke[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) s[n][e][c] = fmaf(ke[e], ue[j][c], s[n][e][c]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    if (jc + c >= V) continue;
+    float* srow = sbase + (size_t)(jc + c) * K;
+#pragma unroll
+    for (int n = 0; n < NF; ++n) {
+      const int i0 = 4 * (lane + L * n);
+      if (k4 && i0 + 3 < K) {
+        *reinterpret_cast<float4*>(srow + i0) = make_float4(s[n][0][c], s[n][1][c], s[n][2][c], s[n][3][c]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (i0 + e < K) srow[i0 + e] = s[n][e][c];
+      }
+    }
+  }
+}
+
+template <int NF>
+int launch_groups(const GroupArgs& a, int n_requests, cudaStream_t stream) {
+  constexpr int COLS = 4 * (SCAN_THREADS / 32);
+  const dim3 grid(n_requests, a.H, (a.V + COLS - 1) / COLS);
+  if (a.kind == DECAY_VECTOR) return launch_pdl(delta_groups_kernel<NF, true>, grid, SCAN_THREADS, 0, stream, a);
+  return launch_pdl(delta_groups_kernel<NF, false>, grid, SCAN_THREADS, 0, stream, a);
+}
+
 static int run_scan(ScanArgs& a, int rows, int n_requests, cudaStream_t stream) {
   const int bx = a.single ? rows : n_requests;
   const int K = a.K;
@@ -807,8 +1113,10 @@ LLM_EXPORT int llm_linear_recurrence(const float* q, int q_stride, const float* 
   a.state = state, a.state_stride = state_stride, a.out = out, a.out_stride = out_stride;
   a.seg = seg, a.row_slot = row_slot;
   a.single = single, a.H = H, a.G = G, a.K = K, a.V = V, a.kind = kind;
-  a.beta = nullptr, a.beta_stride = 0, a.unit = 0, a.unit_floor = 0.f;
-  return run_scan(a, rows, n_requests, stream);
+  a.beta = nullptr, a.beta_stride = 0, a.unit = 0, a.unit_floor = 0.f, a.tail_only = 0;
+  const int rc = run_scan(a, rows, n_requests, stream);
+  if (!single) next_launch_plain();      // (whatever follows the walk of a portion)
+  return rc;
 }
 
 // The gated delta rule over the rows of a step, with the state and the segments of the recurrence
@@ -817,13 +1125,16 @@ LLM_EXPORT int llm_linear_recurrence(const float* q, int q_stride, const float* 
 // a = exp(-exp(p0[h]) softplus(d + p1[h])) for all key channels of head h.  beta [rows][H] is read
 // before its sigmoid.  `unit`: q and k of every head are divided by sqrt(sum of squares + floor)
 // first; q is then multiplied by q_scale.
-LLM_EXPORT int llm_delta_recurrence(const float* q, int q_stride, const float* k, int k_stride, const float* v,
-                                    int v_stride, const float* d, int d_stride, const float* beta,
-                                    int beta_stride, const float* p0, const float* p1, float q_scale, int unit,
-                                    float unit_floor, float* state, long long state_stride, float* out,
-                                    int out_stride, const int* seg, const int* row_slot, int rows,
-                                    int n_requests, int single, int H, int G, int K, int V, int kind,
-                                    cudaStream_t stream) {
+// `work` (work_floats >= rows * H * (4 K + 41) floats, or null): room for what the groups of four
+// tokens need; without it every row goes token by token.
+LLM_EXPORT int llm_delta_recurrence_grouped(const float* q, int q_stride, const float* k, int k_stride,
+                                            const float* v, int v_stride, const float* d, int d_stride,
+                                            const float* beta, int beta_stride, const float* p0, const float* p1,
+                                            float q_scale, int unit, float unit_floor, float* state,
+                                            long long state_stride, float* out, int out_stride, const int* seg,
+                                            const int* row_slot, int rows, int n_requests, int single, int H,
+                                            int G, int K, int V, int kind, float* work, long long work_floats,
+                                            cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G || K <= 0 || V <= 0 || !beta) return LLM_ERR_ARGUMENT;
   if (kind != DECAY_VECTOR && kind != DECAY_RATE_STEP) return LLM_ERR_ARGUMENT;
@@ -837,8 +1148,45 @@ LLM_EXPORT int llm_delta_recurrence(const float* q, int q_stride, const float* k
   a.state = state, a.state_stride = state_stride, a.out = out, a.out_stride = out_stride;
   a.seg = seg, a.row_slot = row_slot;
   a.single = single, a.H = H, a.G = G, a.K = K, a.V = V, a.kind = kind;
-  a.beta = beta, a.beta_stride = beta_stride, a.unit = unit ? 1 : 0, a.unit_floor = unit_floor;
-  return run_scan(a, rows, n_requests, stream);
+  a.beta = beta, a.beta_stride = beta_stride, a.unit = unit ? 1 : 0, a.unit_floor = unit_floor, a.tail_only = 0;
+  // Portions of prompts with 68 to 256 key channels go four tokens at a time: what a group needs
+  // is prepared once per head in parallel over the tokens, the walk takes a group per round, and
+  // the token-by-token kernel takes the rows that are left (fewer than four a request).
+  const long long need = (long long)rows * H * (4LL * K + GROUP_COEF + 1);
+  if (!single && work && work_floats >= need && K > 64 && K <= 256 && (K & 3) == 0) {
+    GroupArgs ga;
+    ga.q = q, ga.q_stride = q_stride, ga.k = k, ga.k_stride = k_stride, ga.v = v, ga.v_stride = v_stride;
+    ga.d = d, ga.d_stride = d_stride, ga.beta = beta, ga.beta_stride = beta_stride, ga.p0 = p0, ga.p1 = p1;
+    ga.q_scale = q_scale, ga.unit = unit ? 1 : 0, ga.unit_floor = unit_floor, ga.seg = seg;
+    ga.H = H, ga.G = G, ga.K = K, ga.V = V, ga.kind = kind;
+    const size_t plane = (size_t)rows * H * K;
+    ga.qa = work, ga.ka = work + plane, ga.kh = work + 2 * plane, ga.at = work + 3 * plane;
+    ga.coef = work + 4 * plane, ga.bs = ga.coef + (size_t)rows * H * GROUP_COEF;
+    ga.state = state, ga.state_stride = state_stride, ga.out = out, ga.out_stride = out_stride;
+    int rc = launch_pdl(delta_prepare_kernel, dim3(n_requests, H, PREPARE_SPLITS), PREPARE_WARPS * 32, 0, stream, ga);
+    if (rc != 0) return rc;
+    next_launch_plain();
+    rc = K <= 128 ? launch_groups<1>(ga, n_requests, stream) : launch_groups<2>(ga, n_requests, stream);
+    if (rc != 0) return rc;
+    a.tail_only = 1;
+    next_launch_plain();
+  }
+  const int rc = run_scan(a, rows, n_requests, stream);
+  if (!single) next_launch_plain();      // (whatever follows the walk of a portion)
+  return rc;
+}
+
+// (the form without room for the groups' preparation: token by token throughout)
+LLM_EXPORT int llm_delta_recurrence(const float* q, int q_stride, const float* k, int k_stride, const float* v,
+                                    int v_stride, const float* d, int d_stride, const float* beta,
+                                    int beta_stride, const float* p0, const float* p1, float q_scale, int unit,
+                                    float unit_floor, float* state, long long state_stride, float* out,
+                                    int out_stride, const int* seg, const int* row_slot, int rows,
+                                    int n_requests, int single, int H, int G, int K, int V, int kind,
+                                    cudaStream_t stream) {
+  return llm_delta_recurrence_grouped(q, q_stride, k, k_stride, v, v_stride, d, d_stride, beta, beta_stride, p0, p1,
+                                      q_scale, unit, unit_floor, state, state_stride, out, out_stride, seg,
+                                      row_slot, rows, n_requests, single, H, G, K, V, kind, nullptr, 0, stream);
 }
 
 // z[r][c] = exp(-exp(rate_log[c / per]) * softplus(z[r][c] + bias[c])) in place: a decay per
@@ -1031,11 +1379,11 @@ LLM_EXPORT int llm_min_gru(float* z, float* u, float* g, int stride, const float
   return LLM_ERR_UNSUPPORTED;
 }
 
-LLM_EXPORT int llm_gated_group_norm_act(const float* o, int o_stride, const float* x, int x_stride,
-                                        const float* skip, int head, const float* g, int g_stride, const float* w,
-                                        int w_period, void* out, int out_dtype, int out_stride, int rows,
-                                        int groups, int group, float eps, int gate_first, int gate_sigmoid,
-                                        cudaStream_t stream) {
+static int gated_group_norm_launch(const float* o, int o_stride, const float* x, int x_stride,
+                                   const float* skip, int head, const float* g, int g_stride, const float* w,
+                                   int w_period, void* out, int out_dtype, int out_stride, int rows,
+                                   int groups, int group, float eps, int gate_first, int gate_sigmoid,
+                                   cudaStream_t stream) {
   if (rows <= 0 || groups <= 0) return 0;
   if (group <= 0 || w_period <= 0 || (skip && (!x || head <= 0))) return LLM_ERR_ARGUMENT;
   const long long items = (long long)rows * groups;
@@ -1081,10 +1429,28 @@ LLM_EXPORT int llm_gated_group_norm_act(const float* o, int o_stride, const floa
   return LLM_ERR_UNSUPPORTED;
 }
 
+LLM_EXPORT int llm_gated_group_norm_act(const float* o, int o_stride, const float* x, int x_stride,
+                                        const float* skip, int head, const float* g, int g_stride, const float* w,
+                                        int w_period, void* out, int out_dtype, int out_stride, int rows,
+                                        int groups, int group, float eps, int gate_first, int gate_sigmoid,
+                                        cudaStream_t stream);
+
 LLM_EXPORT int llm_gated_group_norm(const float* o, int o_stride, const float* x, int x_stride,
                                     const float* skip, int head, const float* g, int g_stride, const float* w,
                                     int w_period, void* out, int out_dtype, int out_stride, int rows,
                                     int groups, int group, float eps, int gate_first, cudaStream_t stream) {
   return llm_gated_group_norm_act(o, o_stride, x, x_stride, skip, head, g, g_stride, w, w_period, out, out_dtype,
                                   out_stride, rows, groups, group, eps, gate_first, 0, stream);
+}
+
+// (a kernel of many blocks that stands in front of the output projection: see launched_many_blocks)
+LLM_EXPORT int llm_gated_group_norm_act(const float* o, int o_stride, const float* x, int x_stride,
+                                        const float* skip, int head, const float* g, int g_stride, const float* w,
+                                        int w_period, void* out, int out_dtype, int out_stride, int rows,
+                                        int groups, int group, float eps, int gate_first, int gate_sigmoid,
+                                        cudaStream_t stream) {
+  const int rc = gated_group_norm_launch(o, o_stride, x, x_stride, skip, head, g, g_stride, w, w_period, out,
+                                         out_dtype, out_stride, rows, groups, group, eps, gate_first, gate_sigmoid,
+                                         stream);
+  return launched_many_blocks(rc, (long long)rows * groups);
 }

@@ -122,6 +122,8 @@ def _signatures():
         "llm_channel_gate": [P, I, P, I, I, I, I, P],
         "llm_delta_recurrence": [P, I, P, I, P, I, P, I, P, I, P, P, F, I, F, P, L, P, I, P, P, I,
                                  I, I, I, I, I, I, I, P],
+        "llm_delta_recurrence_grouped": [P, I, P, I, P, I, P, I, P, I, P, P, F, I, F, P, L, P, I, P,
+                                         P, I, I, I, I, I, I, I, I, P, L, P],
         "llm_rate_decay": [P, P, P, I, I, I, P],
         "llm_moe_router_scaled": [P, I, P, P, P, I, I, I, I, I, I, I, P, P, P, F, P],
         "llm_moe_route_scaled": [P, I, I, I, I, I, P, P, P, F, P],
@@ -528,7 +530,8 @@ def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d: torch
                      key_dim: int, value_dim: int, kind: int, q_scale: float = 1.0,
                      unit_floor: Optional[float] = None,
                      rate_log: Optional[torch.Tensor] = None,
-                     step_bias: Optional[torch.Tensor] = None, n_requests: int = 0) -> None:
+                     step_bias: Optional[torch.Tensor] = None, n_requests: int = 0,
+                     work: Optional[torch.Tensor] = None) -> None:
     """The gated delta rule per request and head over the rows of the step in order:
     ``S <- diag(a_t) S``, ``u = sigmoid(beta_t) (v_t - S^T k_t)``, ``S <- S + k_t u^T``,
     ``o_t = S^T q_t``.  Tensors, state and ``seg`` as in :func:`linear_recurrence`; ``beta``
@@ -536,20 +539,38 @@ def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d: torch
     [rows, heads * key_dim] is the decay; DECAY_RATE_STEP: ``d`` [rows, heads] and
     ``a = exp(-exp(rate_log[h]) softplus(d + step_bias[h]))`` for every key channel of head h.
     ``unit_floor`` (not None): q and k of every head are first divided by
-    ``sqrt(sum of squares + unit_floor)``; q is then multiplied by ``q_scale``."""
-    _cuda(q, k, v, d, beta, state, out, row_slot, seg, rate_log, step_bias)
+    ``sqrt(sum of squares + unit_floor)``; q is then multiplied by ``q_scale``.
+    ``work`` (float32, at least :func:`delta_work_floats` elements): room for what portions of
+    prompts need to go four tokens at a time (68 to 256 key channels, a multiple of four);
+    without it, and for single tokens, every row goes token by token.  The two ways differ by
+    rounding only."""
+    _cuda(q, k, v, d, beta, state, out, row_slot, seg, rate_log, step_bias, work)
+    assert work is None or (work.dtype == torch.float32 and work.is_contiguous())
     for t in (q, k, v, d, beta, state, out):
         assert t.dtype == torch.float32 and t.stride(-1) == 1
     rows = out.shape[0]
     assert state.dim() == 2 and state.shape[1] >= heads * value_dim * key_dim
     assert kind in (DECAY_VECTOR, DECAY_RATE_STEP)
-    _check(lib().llm_delta_recurrence(
+    _check(lib().llm_delta_recurrence_grouped(
         _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(d), d.stride(0),
         _ptr(beta), beta.stride(0), _ptr(rate_log), _ptr(step_bias), float(q_scale),
         int(unit_floor is not None), float(unit_floor or 0.0), _ptr(state), state.stride(0),
         _ptr(out), out.stride(0), _ptr(seg), _ptr(row_slot), rows, int(n_requests),
-        int(seg is None), heads, groups, key_dim, value_dim, kind, _stream()),
+        int(seg is None), heads, groups, key_dim, value_dim, kind, _ptr(work),
+        work.numel() if work is not None else 0, _stream()),
         f"delta_recurrence (key_dim {key_dim})")
+    global launches
+    if work is not None and seg is not None and delta_work_floats(rows, heads, key_dim) \
+            and work.numel() >= delta_work_floats(rows, heads, key_dim):
+        launches += 2      # the groups' preparation and their walk are launches of their own
+
+
+def delta_work_floats(rows: int, heads: int, key_dim: int) -> int:
+    """Elements of the ``work`` buffer with which :func:`delta_recurrence` takes the rows of a
+    step four tokens at a time, 0 when it has no such form for this many key channels."""
+    if not (64 < key_dim <= 256 and key_dim % 4 == 0):
+        return 0
+    return rows * heads * (4 * key_dim + 41)
 
 
 def causal_conv_silu(src: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],

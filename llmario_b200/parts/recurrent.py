@@ -412,10 +412,14 @@ class GatedDeltaRule:
             d = proj[:, self.col["a"]:self.col["a"] + H]
             kind, rate, bias = kernels.DECAY_RATE_STEP, self.rate_log, self.step_bias
         o = ctx.buffer("delta.o", (rows, H * V), torch.float32)
+        # (portions of prompts go four tokens at a time where the kernels have that form)
+        work = None
+        if seg is not None and kernels.delta_work_floats(rows, H, K):
+            work = ctx.buffer("delta.work", (kernels.delta_work_floats(rows, H, K),), torch.float32)
         kernels.delta_recurrence(
             conv[:, :G * K], conv[:, G * K:2 * G * K], conv[:, 2 * G * K:], d, beta, state, o,
             ctx.row_slot, seg, H, G, K, V, kind, q_scale=K ** -0.5, unit_floor=self.UNIT_FLOOR,
-            rate_log=rate, step_bias=bias, n_requests=len(ctx.segments))
+            rate_log=rate, step_bias=bias, n_requests=len(ctx.segments), work=work)
         if self.gate_low_rank:
             gate = ctx.buffer("delta.gate", (rows, H * V), torch.float32)
             self._second(ctx, proj, "g", self.gate_proj, gate)

@@ -162,12 +162,14 @@ def _segments(rows_per_slot, n_slots):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("per_channel", (False, True))
+@pytest.mark.parametrize("grouped", (False, True))
 @pytest.mark.parametrize("H,G,K,V", [(2, 1, 8, 5), (3, 3, 24, 16), (4, 2, 64, 32), (2, 2, 100, 33),
                                      (6, 2, 128, 64), (1, 1, 136, 24), (2, 1, 256, 20),
-                                     (1, 1, 320, 130)])
-def test_delta_rule_kernel(H, G, K, V, per_channel):
+                                     (3, 1, 68, 17), (1, 1, 320, 130)])
+def test_delta_rule_kernel(H, G, K, V, per_channel, grouped):
     """Steps of unequal requests with the state carried in the slots, then single tokens; unit
-    vectors and the scale of q made by the kernel; both ways to make the decay."""
+    vectors and the scale of q made by the kernel; both ways to make the decay; token by token
+    and (``grouped``, where the kernels have that form) four tokens at a time."""
     from llmario_b200 import kernels
 
     rng = np.random.default_rng(K + V)
@@ -189,17 +191,20 @@ def test_delta_rule_kernel(H, G, K, V, per_channel):
         dev = lambda a: torch.tensor(a, dtype=torch.float32, device="cuda")
         row_slot, seg = _segments(plan, n_slots)
         out = torch.empty(rows, H * V, device="cuda")
+        work = None
+        if grouped and kernels.delta_work_floats(rows, H, K):
+            work = torch.full((kernels.delta_work_floats(rows, H, K),), float("nan"), device="cuda")
         if per_channel:
             d = dev(z)
             kernels.rate_decay(d, dev(rate_log), dev(bias), K)
             kernels.delta_recurrence(dev(q), dev(k), dev(v), d, dev(beta), state, out, row_slot,
                                      None if single else seg, H, G, K, V, kernels.DECAY_VECTOR,
-                                     q_scale=K ** -0.5, unit_floor=1e-6, n_requests=len(plan))
+                                     q_scale=K ** -0.5, unit_floor=1e-6, n_requests=len(plan), work=work)
         else:
             kernels.delta_recurrence(dev(q), dev(k), dev(v), dev(z), dev(beta), state, out, row_slot,
                                      None if single else seg, H, G, K, V, kernels.DECAY_RATE_STEP,
                                      q_scale=K ** -0.5, unit_floor=1e-6, rate_log=dev(rate_log),
-                                     step_bias=dev(bias), n_requests=len(plan))
+                                     step_bias=dev(bias), n_requests=len(plan), work=work)
         got = out.cpu().numpy().astype(np.float64)
         r0 = 0
         for s, n in plan:
